@@ -1,0 +1,59 @@
+"""ctypes binding of the C ABI in ``include/decx_b200.h``.
+
+The shared library is built in-tree by ``decx_b200.build`` (nvcc, sm_100a).  There is no
+fallback of any kind: if the library is missing, importing this module raises, and if a call
+fails the error code is turned into ``DecxB200Error``.
+"""
+import ctypes
+import os
+
+FP32, FP16, CPLXF = 1, 3, 5
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libdecx_b200.so")
+
+
+class DecxB200Error(RuntimeError):
+    def __init__(self, code, what):
+        super().__init__(f"decx_b200 error {code}: {what}")
+        self.code = code
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m decx_b200.build` "
+            "(there is no CPU or PyTorch fallback for the GEMM path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    u32, u64, vp, sz, ci = (ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int)
+    lib.decxb200_gemm_workspace_bytes.restype = sz
+    lib.decxb200_gemm_workspace_bytes.argtypes = [ci, u32, u32, u32]
+    gemm_args = [ci, vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
+    lib.decxb200_gemm.restype = ci
+    lib.decxb200_gemm.argtypes = gemm_args
+    lib.decxb200_gemm_ex.restype = ci
+    lib.decxb200_gemm_ex.argtypes = gemm_args + [ci, ci]
+    lib.decxb200_last_launch_count.restype = ci
+    lib.decxb200_last_launch_count.argtypes = []
+    lib.decxb200_strerror.restype = ctypes.c_char_p
+    lib.decxb200_strerror.argtypes = [ci]
+    lib.decxb200_version.restype = ctypes.c_char_p
+    lib.decxb200_version.argtypes = []
+    return lib
+
+
+lib = _load()
+
+EXPORTS = [
+    "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
+    "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
+]
+
+
+def check(code):
+    if code != 0:
+        raise DecxB200Error(code, lib.decxb200_strerror(code).decode())
+
+
+def workspace_bytes(dtype, M, N, K):
+    return int(lib.decxb200_gemm_workspace_bytes(dtype, M, N, K))

@@ -1,0 +1,422 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D(M x N) = alpha * A(M x K) * B(K x N) + beta * C(M x N)         row-major, pitched
+//
+// replaces the SIMT kernels behind de::blas::cuda::GEMM
+// (srcs/modules/BLAS/GEMM/CUDA/large_squares/{fp32,fp16,64b}/*_kernels.cu in the
+// reference: 256-thread CTAs, one shared-memory stage, FMA inner loop) with:
+//
+//   warp 0      TMA producer: 128-byte-swizzled tiles of A (K-major) and of row-major
+//               B (consumed MN-major, so B is never transposed) into a ring of stages
+//   warp 1      allocates TMEM and issues tcgen05.mma; fp32 accumulators live in TMEM,
+//               two of them, so the epilogue of tile i overlaps the main loop of i+1
+//   warps 2..5  epilogue: tcgen05.ld -> alpha/beta/C -> global stores (predicated edges)
+//
+// KIND 0  fp16 operands, kind::f16, fp16 output.
+// KIND 1  fp32 operands pre-split into tf32 (hi, lo) planes, kind::tf32, three MMAs per
+//         K step (lo*hi, hi*lo, hi*hi) into one accumulator = "3xTF32"; fp32 output.
+//         Interleaved complex problems arrive here as a real problem of twice the K and
+//         N extents (see prepass.cuh), only the epilogue knows about (re, im) pairs.
+// CTAS 1  one CTA per 128 x 256 tile.
+// CTAS 2  a CTA pair (cluster of 2) per 256 x 256 tile, tcgen05 cta_group::2: each CTA
+//         loads its own 128 rows of A and its own 128 columns of B (no multicast), the
+//         pair's leader issues the MMAs, each CTA keeps its 128 x 256 accumulator rows.
+//
+// Ragged M/N/K: tensor maps carry the logical extents, so out-of-range parts of a box
+// are zero-filled by TMA; stores are predicated.  No host-side padding.
+// Every wait is bounded: on time-out the role writes a code to *status and unwinds.
+#pragma once
+#include <cuda_fp16.h>
+#include "sm100_ptx.cuh"
+
+namespace dxb {
+
+enum EpilogueMode : int { EPI_REAL = 0, EPI_COMPLEX = 1 };
+
+// status codes written by the kernel (0 = ok)
+enum KernelStatus : unsigned {
+    KS_OK = 0,
+    KS_TIMEOUT_PRODUCER = 0x101,
+    KS_TIMEOUT_MMA_FULL = 0x102,
+    KS_TIMEOUT_MMA_ACC = 0x103,
+    KS_TIMEOUT_EPILOGUE = 0x104,
+    KS_TIMEOUT_TAIL = 0x105,
+};
+
+struct GemmParams {
+    uint32_t M, N, K;          // real problem extents seen by the MMA (complex: N, K doubled)
+    void* D;                   // fp16 (KIND 0) or fp32 (KIND 1)
+    const void* C;             // same type as D, or nullptr
+    uint64_t ldd, ldc;         // in scalars of the output type
+    float alpha_re, alpha_im, beta_re, beta_im;
+    int epi_mode;              // EpilogueMode
+    int vec_d, vec_c;          // 1 if 16-byte vector access to D / C rows is legal
+    uint32_t tiles_m, tiles_n; // in units of (128*CTAS) x 256
+    uint32_t group_m;          // rasterisation group height, in tiles
+    unsigned* status;          // device word, may be nullptr
+    unsigned long long wait_limit_ns;
+};
+
+template <int KIND, int CTAS>
+struct GemmCfg {
+    static constexpr int ELEM = (KIND == 0) ? 2 : 4;
+    static constexpr int NPL = (KIND == 0) ? 1 : 2;       // operand planes (hi, lo)
+    static constexpr int BM = 128;                        // rows per CTA
+    static constexpr int BN = 256;                        // UMMA N
+    static constexpr int BN_LOAD = BN / CTAS;             // columns of B this CTA loads
+    static constexpr int BK = 128 / ELEM;                 // one 128-byte swizzle row of K
+    static constexpr int UMMA_K = 32 / ELEM;
+    static constexpr int CHUNK_N = 128 / ELEM;            // B columns per 128-byte row
+    static constexpr int B_CHUNKS = BN_LOAD / CHUNK_N;
+    static constexpr int A_TILE = BM * 128;               // bytes per plane
+    static constexpr int B_CHUNK_BYTES = BK * 128;
+    static constexpr int B_TILE = B_CHUNKS * B_CHUNK_BYTES;
+    static constexpr int STAGE = NPL * (A_TILE + B_TILE);
+    static constexpr int STAGES = (192 * 1024) / STAGE;
+    static constexpr int TMEM_COLS = 512;                 // two 256-column accumulators
+    static constexpr int THREADS = 192;
+    static constexpr int SMEM_BYTES = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
+};
+
+// tile index -> (tile_m, tile_n), walking groups of `group_m` tile rows column by column
+// so that the CTAs running at one time share a small set of A rows and B columns in L2.
+__device__ __forceinline__ void tile_coords(uint32_t t, const GemmParams& p, uint32_t& tm, uint32_t& tn) {
+    const uint32_t per_group = p.group_m * p.tiles_n;
+    const uint32_t g = t / per_group;
+    const uint32_t first_m = g * p.group_m;
+    const uint32_t rows = min(p.group_m, p.tiles_m - first_m);
+    const uint32_t r = t - g * per_group;
+    tm = first_m + r % rows;
+    tn = r / rows;
+}
+
+__device__ __forceinline__ void report(const GemmParams& p, unsigned code) {
+    if (p.status != nullptr) atomicCAS(p.status, 0u, code);
+}
+
+template <int KIND>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, const uint32_t (&v)[32]) {
+    // v holds the fp32 accumulators of columns col0 .. col0+31 of `row`
+    const bool has_c = (p.C != nullptr);
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(v[i]);
+    const uint32_t ncols = min(32u, p.N - col0);
+
+    if constexpr (KIND == 0) {
+        __half* drow = reinterpret_cast<__half*>(p.D) + size_t(row) * p.ldd + col0;
+        const __half* crow = has_c ? reinterpret_cast<const __half*>(p.C) + size_t(row) * p.ldc + col0 : nullptr;
+        const bool scale = has_c || p.alpha_re != 1.0f;
+        if (scale) {
+            if (has_c) {
+                if (ncols == 32 && p.vec_c) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 c4 = __ldg(reinterpret_cast<const uint4*>(crow) + q);
+                        const __half2* h = reinterpret_cast<const __half2*>(&c4);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __half22float2(h[j]);
+                            acc[q * 8 + 2 * j] = p.alpha_re * acc[q * 8 + 2 * j] + p.beta_re * f.x;
+                            acc[q * 8 + 2 * j + 1] = p.alpha_re * acc[q * 8 + 2 * j + 1] + p.beta_re * f.y;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i < ncols) acc[i] = p.alpha_re * acc[i] + p.beta_re * __half2float(crow[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] *= p.alpha_re;
+            }
+        }
+        if (ncols == 32 && p.vec_d) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(acc[q * 8 + 2 * j], acc[q * 8 + 2 * j + 1]);
+                reinterpret_cast<uint4*>(drow)[q] = o;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < ncols) drow[i] = __float2half_rn(acc[i]);
+        }
+    } else {
+        float* drow = reinterpret_cast<float*>(p.D) + size_t(row) * p.ldd + col0;
+        const float* crow = has_c ? reinterpret_cast<const float*>(p.C) + size_t(row) * p.ldc + col0 : nullptr;
+        if (p.epi_mode == EPI_REAL) {
+            if (has_c) {
+                if (ncols == 32 && p.vec_c) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 c4 = __ldg(reinterpret_cast<const float4*>(crow) + q);
+                        acc[4 * q + 0] = p.alpha_re * acc[4 * q + 0] + p.beta_re * c4.x;
+                        acc[4 * q + 1] = p.alpha_re * acc[4 * q + 1] + p.beta_re * c4.y;
+                        acc[4 * q + 2] = p.alpha_re * acc[4 * q + 2] + p.beta_re * c4.z;
+                        acc[4 * q + 3] = p.alpha_re * acc[4 * q + 3] + p.beta_re * c4.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i < ncols) acc[i] = p.alpha_re * acc[i] + p.beta_re * crow[i];
+                }
+            } else if (p.alpha_re != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] *= p.alpha_re;
+            }
+        } else {
+            // (re, im) pairs sit in adjacent columns; col0 and N are even here
+            const bool scale = has_c || p.alpha_re != 1.0f || p.alpha_im != 0.0f;
+            if (scale) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float re = acc[i], im = acc[i + 1];
+                    float ore = p.alpha_re * re - p.alpha_im * im;
+                    float oim = p.alpha_re * im + p.alpha_im * re;
+                    if (has_c && i < ncols) {
+                        const float2 c2 = __ldg(reinterpret_cast<const float2*>(crow + i));
+                        ore += p.beta_re * c2.x - p.beta_im * c2.y;
+                        oim += p.beta_re * c2.y + p.beta_im * c2.x;
+                    }
+                    acc[i] = ore;
+                    acc[i + 1] = oim;
+                }
+            }
+        }
+        if (ncols == 32 && p.vec_d) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                reinterpret_cast<float4*>(drow)[q] =
+                    make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < ncols) drow[i] = acc[i];
+        }
+    }
+}
+
+template <int KIND, int CTAS>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                    const GemmParams p) {
+    using Cfg = GemmCfg<KIND, CTAS>;
+    constexpr int STAGES = Cfg::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE;
+    const uint32_t full_bar = bar_base;                      // STAGES x 8 B
+    const uint32_t empty_bar = bar_base + 8 * STAGES;        // STAGES x 8 B
+    const uint32_t accf_bar = bar_base + 16 * STAGES;        // 2 x 8 B  accumulator full
+    const uint32_t acce_bar = accf_bar + 16;                 // 2 x 8 B  accumulator empty
+    const uint32_t tmem_slot = acce_bar + 16;                // 4 B
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+    const bool leader = (cta_rank == 0);
+    const uint32_t n_workers = gridDim.x / CTAS;             // CTAs (or pairs) walking the tile list
+    const uint32_t worker = blockIdx.x / CTAS;
+    const uint32_t n_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t n_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+    const uint64_t limit = p.wait_limit_ns;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(accf_bar + 8 * a, 1);
+            mbar_init(acce_bar + 8 * a, 4 * CTAS);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<CTAS>(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before_sync();
+    if constexpr (CTAS == 2) cluster_sync_all(); else __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA0);
+            tma_prefetch_desc(&tmB0);
+            if constexpr (KIND == 1) { tma_prefetch_desc(&tmA1); tma_prefetch_desc(&tmB1); }
+            const uint32_t full_target = (CTAS == 2) ? map_to_cta(full_bar, 0) : full_bar;
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
+                uint32_t tm, tn;
+                tile_coords(t, p, tm, tn);
+                const int32_t row0 = int32_t((tm * CTAS + cta_rank) * Cfg::BM);
+                const int32_t col0 = int32_t(tn * Cfg::BN + cta_rank * Cfg::BN_LOAD);
+                for (uint32_t kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait_bounded(empty_bar + 8 * s, ph ^ 1u, limit)) {
+                        report(p, KS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t stage = smem_base + s * Cfg::STAGE;
+                    const uint32_t fb = full_target + 8 * s;
+                    if (leader) mbar_arrive_expect_tx(full_bar + 8 * s, uint32_t(Cfg::STAGE) * CTAS);
+                    const int32_t k0 = int32_t(kb * Cfg::BK);
+#pragma unroll
+                    for (int pl = 0; pl < Cfg::NPL; ++pl) {
+                        const CUtensorMap* ma = (pl == 0) ? &tmA0 : &tmA1;
+                        const CUtensorMap* mb = (pl == 0) ? &tmB0 : &tmB1;
+                        const uint32_t a_dst = stage + pl * Cfg::A_TILE;
+                        const uint32_t b_dst = stage + Cfg::NPL * Cfg::A_TILE + pl * Cfg::B_TILE;
+                        if constexpr (CTAS == 2) tma_load_2d_pair(a_dst, ma, fb, k0, row0);
+                        else tma_load_2d(a_dst, ma, fb, k0, row0);
+#pragma unroll
+                        for (int j = 0; j < Cfg::B_CHUNKS; ++j) {
+                            if constexpr (CTAS == 2)
+                                tma_load_2d_pair(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
+                            else
+                                tma_load_2d(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
+                        }
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+            // tail: every stage this CTA filled has been released by the MMA side, so no
+            // arrival (possibly from the peer CTA) can land after this CTA has exited
+            if (ok) {
+                for (int i = 0; i < STAGES; ++i) {
+                    if (!mbar_wait_bounded(empty_bar + 8 * s, ph ^ 1u, limit)) {
+                        report(p, KS_TIMEOUT_TAIL);
+                        break;
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (leader && lane == 0) {
+            constexpr uint64_t DESC_A = smem_desc_sw128(16, 1024);                    // K-major: 8-row groups 1024 B apart
+            constexpr uint64_t DESC_B = smem_desc_sw128(Cfg::B_CHUNK_BYTES, 1024);    // MN-major: chunk stride / 8-k-row stride
+            constexpr uint32_t A_KSTEP = 32;                                          // UMMA_K elements along a 128 B row
+            constexpr uint32_t B_KSTEP = Cfg::UMMA_K * 128;                           // UMMA_K rows of 128 B
+            const uint32_t peer_empty = (CTAS == 2) ? map_to_cta(empty_bar, 1) : 0u;
+            const uint32_t peer_accf = (CTAS == 2) ? map_to_cta(accf_bar, 1) : 0u;
+            uint32_t s = 0, ph = 0, it = 0;
+            bool ok = true;
+            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++it) {
+                const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
+                    report(p, KS_TIMEOUT_MMA_ACC);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + a * Cfg::BN;
+                for (uint32_t kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait_bounded(full_bar + 8 * s, ph, limit)) {
+                        report(p, KS_TIMEOUT_MMA_FULL);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t stage = smem_base + s * Cfg::STAGE;
+                    const uint32_t a0 = stage, b0 = stage + Cfg::NPL * Cfg::A_TILE;
+#pragma unroll
+                    for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
+                        const uint32_t acc_flag = (kb | uint32_t(k)) ? 1u : 0u;
+                        if constexpr (KIND == 0) {
+                            umma_ss<0, CTAS>(d_tmem, smem_desc_at(DESC_A, a0 + k * A_KSTEP),
+                                             smem_desc_at(DESC_B, b0 + k * B_KSTEP), Cfg::IDESC, acc_flag);
+                        } else {
+                            const uint64_t a_hi = smem_desc_at(DESC_A, a0 + k * A_KSTEP);
+                            const uint64_t a_lo = smem_desc_at(DESC_A, a0 + Cfg::A_TILE + k * A_KSTEP);
+                            const uint64_t b_hi = smem_desc_at(DESC_B, b0 + k * B_KSTEP);
+                            const uint64_t b_lo = smem_desc_at(DESC_B, b0 + Cfg::B_TILE + k * B_KSTEP);
+                            // small terms first, the dominant hi*hi product last
+                            umma_ss<1, CTAS>(d_tmem, a_lo, b_hi, Cfg::IDESC, acc_flag);
+                            umma_ss<1, CTAS>(d_tmem, a_hi, b_lo, Cfg::IDESC, 1u);
+                            umma_ss<1, CTAS>(d_tmem, a_hi, b_hi, Cfg::IDESC, 1u);
+                        }
+                    }
+                    umma_commit<CTAS>(empty_bar + 8 * s);                 // stage free once these MMAs retire
+                    if constexpr (CTAS == 2) umma_commit<CTAS>(peer_empty + 8 * s);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) {
+                    umma_commit<CTAS>(accf_bar + 8 * a);                  // accumulator complete
+                    if constexpr (CTAS == 2) umma_commit<CTAS>(peer_accf + 8 * a);
+                }
+            }
+            // tail: both accumulators drained by every epilogue warp (of both CTAs)
+            if (ok) {
+                for (int i = 0; i < 2; ++i, ++it) {
+                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                    if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
+                        report(p, KS_TIMEOUT_TAIL);
+                        break;
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
+        const uint32_t acce_target = (CTAS == 2) ? map_to_cta(acce_bar, 0) : acce_bar;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++it) {
+            uint32_t tm, tn;
+            tile_coords(t, p, tm, tn);
+            const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+            if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
+                if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t row = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32 + lane;
+            const uint32_t colbase = tn * Cfg::BN;
+            const uint32_t taddr = tmem_base + a * Cfg::BN + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (uint32_t c = 0; c < Cfg::BN / 32; ++c) {
+                const uint32_t col0 = colbase + c * 32;
+                if (col0 >= p.N) break;                      // uniform across the warp
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_ld_wait();
+                if (row < p.M) store_chunk<KIND>(p, row, col0, v);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CTAS == 2) mbar_arrive_cluster(acce_target + 8 * a);
+                else mbar_arrive(acce_bar + 8 * a);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+    }
+    if constexpr (CTAS == 2) cluster_sync_all();
+}
+
+}  // namespace dxb

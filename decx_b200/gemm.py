@@ -1,0 +1,68 @@
+"""Device-tensor front end of the C ABI, used by the tests and the benchmark.
+
+``gemm(A, B, C, alpha, beta)`` has the meaning of the reference's
+``de::blas::cuda::GEMM(GPU_Matrix& A, B, [C,] dst[, alpha, beta])``
+(srcs/modules/BLAS/GEMM/CUDA/GEMM_LS.cu:315-393): ``dst = A.B`` or ``dst = alpha.A.B + beta.C`` on
+row-major pitched device matrices; fp16 accumulates in fp32 and returns fp16.  torch is used only
+to own device memory and the stream; the arithmetic is the library's tcgen05 kernels.
+"""
+import ctypes
+
+import torch
+
+from . import capi
+
+_DTYPES = {torch.float32: capi.FP32, torch.float16: capi.FP16, torch.complex64: capi.CPLXF}
+
+
+def _ld(t):
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError("matrices must be 2-D with unit column stride (row-major, pitched)")
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0))
+
+
+def _scalar(dtype, v):
+    if v is None:
+        return None, None
+    if dtype == capi.CPLXF:
+        c = complex(v)
+        buf = (ctypes.c_float * 2)(c.real, c.imag)
+    else:
+        buf = (ctypes.c_float * 1)(float(v))
+    return buf, ctypes.cast(buf, ctypes.c_void_p)
+
+
+def new_status(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def gemm(A, B, C=None, alpha=None, beta=None, out=None, workspace=None, status=None, cta_group=0, max_ctas=0):
+    """Launch on torch's current stream of A's device; returns ``out`` (asynchronous)."""
+    if not A.is_cuda:
+        raise RuntimeError("decx_b200.gemm works on CUDA tensors only (no CPU fallback)")
+    dt = _DTYPES.get(A.dtype)
+    if dt is None or B.dtype != A.dtype or (C is not None and C.dtype != A.dtype):
+        raise TypeError("A, B, C must share one dtype out of float16, float32, complex64")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"A is {M}x{K} but B is {K2}x{N}")
+    if C is not None and tuple(C.shape) != (M, N):
+        raise ValueError("C must be M x N")
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    need = capi.workspace_bytes(dt, M, N, K)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=A.device)
+    with torch.cuda.device(A.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _a, pa = _scalar(dt, alpha)
+        _b, pb = _scalar(dt, beta if C is not None else None)
+        code = capi.lib.decxb200_gemm_ex(
+            dt, stream, M, N, K, A.data_ptr(), _ld(A), B.data_ptr(), _ld(B),
+            C.data_ptr() if C is not None else None, _ld(C) if C is not None else 0,
+            out.data_ptr(), _ld(out), pa, pb,
+            workspace.data_ptr() if need else None, need,
+            status.data_ptr() if status is not None else None, cta_group, max_ctas)
+    capi.check(code)
+    return out

@@ -1,0 +1,101 @@
+/*
+ * decx_b200 -- C ABI of the B200 (sm_100a) dense-GEMM path.
+ *
+ * This is the boundary a DECX build binds to replace its BLAS-CUDA GEMM kernels.
+ * Plain pointers and sizes only; no C++ or framework types.  All matrices are
+ * row-major with a row pitch ("ld") counted in ELEMENTS of the matrix type
+ * (an element of a complex matrix is one {re, im} pair).
+ *
+ * Every function returns 0 on success, a negative DECXB200_E* code for an invalid
+ * argument or a missing capability, or a positive cudaError_t value.  Nothing in this
+ * library calls exit(), throws, or falls back to a host computation.
+ */
+#ifndef DECX_B200_H_
+#define DECX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DECXB200_API __attribute__((visibility("default")))
+#else
+#define DECXB200_API
+#endif
+
+/* element types; the values are de::_DATA_TYPES_FLAGS_
+ * (reference: srcs/includes/DECX/classes/type_info.h:20-43) */
+#define DECXB200_FP32 1
+#define DECXB200_FP16 3
+#define DECXB200_CPLXF 5
+
+#define DECXB200_EINVAL (-1)       /* null pointer, zero extent, unknown dtype            */
+#define DECXB200_EALIGN (-2)       /* fp16 operand pitch/base not 16-byte aligned (TMA)    */
+#define DECXB200_EWORKSPACE (-3)   /* workspace missing, misaligned or too small           */
+#define DECXB200_EDRIVER (-4)      /* cuTensorMapEncodeTiled unavailable / failed          */
+#define DECXB200_ETOOLARGE (-5)    /* extent beyond what the entry point supports          */
+#define DECXB200_EKERNEL (-6)      /* the kernel reported a time-out through its status word */
+
+/*
+ * Scratch bytes decxb200_gemm needs for one problem (0 for fp16).
+ * fp32:  tf32 (hi, lo) planes of A and B.
+ * cplxf: (hi, lo) planes of A viewed as M x 2K reals and of the 2K x 2N real
+ *        expansion of B.
+ * Replaces the planner-owned A-transpose scratch of the reference
+ * (srcs/modules/BLAS/GEMM/CUDA/large_squares/common/cuda_GEMM_LS_planner.cu:125-127,156-163).
+ */
+DECXB200_API size_t decxb200_gemm_workspace_bytes(int dtype, uint32_t M, uint32_t N, uint32_t K);
+
+/*
+ * D = alpha * A * B + beta * C   on the current device, asynchronously on `stream`.
+ *
+ *   A: M x K (lda), B: K x N (ldb), C: M x N (ldc) or NULL, D: M x N (ldd); device pointers.
+ *   alpha, beta: host pointers to one element of the accumulate type (float for fp32 and
+ *                fp16, float[2] = {re, im} for cplxf); NULL means 1 (alpha) / 0 (beta).
+ *                C is not read when it is NULL or beta == 0.
+ *   workspace:   device scratch of at least decxb200_gemm_workspace_bytes(), 256-byte
+ *                aligned; may be NULL for fp16.
+ *   status:      device word the kernel writes a non-zero code to if one of its bounded
+ *                waits expires (never expected); may be NULL.  Must be zero before the call.
+ *
+ * Replaces the uniform kernel-caller signature of the reference,
+ * decx::blas::_cu_GEMM_kernel_ptr<T>
+ * (srcs/modules/BLAS/GEMM/CUDA/large_squares/common/cuda_GEMM_LS_planner.cuh:64-69) and the
+ * callers behind it (fp32/GEMM_fp32_callers.cuh:75-215, fp16/GEMM_fp16_callers.cuh:57-128,
+ * 64b/GEMM_64b_callers.cuh:78-98).  fp16 accumulates in fp32 and stores fp16.
+ * fp32 and cplxf run as 3xTF32 and keep fp32 accuracy.
+ */
+DECXB200_API int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K,
+                               const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                               const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                               const void* alpha, const void* beta,
+                               void* workspace, size_t workspace_bytes, unsigned* status);
+
+/*
+ * Same, with the tuning knobs exposed (tests and the benchmark use them):
+ *   cta_group: 0 = library default, 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile
+ *   max_ctas:  upper bound on the persistent grid (0 = number of SMs)
+ */
+DECXB200_API int decxb200_gemm_ex(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K,
+                                  const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                                  const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                                  const void* alpha, const void* beta,
+                                  void* workspace, size_t workspace_bytes, unsigned* status,
+                                  int cta_group, int max_ctas);
+
+/* Number of kernels the last decxb200_gemm* call of this thread launched (pre-passes included). */
+DECXB200_API int decxb200_last_launch_count(void);
+
+/* Static description of an error code returned by this library. */
+DECXB200_API const char* decxb200_strerror(int code);
+
+/* Library version, "major.minor". */
+DECXB200_API const char* decxb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECX_B200_H_ */
