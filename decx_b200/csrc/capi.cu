@@ -45,9 +45,9 @@ thread_local int t_launches = 0;
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
 // 2-D row-major tensor (rows x cols, `ld` elements per row) with a (box_cols x box_rows) box,
-// 128-byte swizzle, zero fill outside [0, cols) x [0, rows).
+// 128-byte swizzle (of 16-byte units unless `swizzle` says otherwise), zero fill outside [0, cols) x [0, rows).
 int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-             uint32_t box_cols, uint32_t box_rows) {
+             uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return DECXB200_EDRIVER;
     const uint64_t esz = f16 ? 2 : 4;
@@ -57,7 +57,7 @@ int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
@@ -250,8 +250,8 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
     using C1 = GemmCfg<1, 1>;
     if ((rc = make_map(&a0, false, a_hi, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
     if ((rc = make_map(&a1, false, a_lo, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
-    if ((rc = make_map(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK)) != 0) return rc;
-    if ((rc = make_map(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK)) != 0) return rc;
+    if ((rc = make_map(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0) return rc;
+    if ((rc = make_map(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0) return rc;
     return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
                           : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);
 }

@@ -309,8 +309,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (leader && lane == 0) {
-            constexpr uint64_t DESC_A = smem_desc_sw128(16, 1024);                    // K-major: 8-row groups 1024 B apart
-            constexpr uint64_t DESC_B = smem_desc_sw128(Cfg::B_CHUNK_BYTES, 1024);    // MN-major: chunk stride / 8-k-row stride
+            // A, K-major: rows of 128 B, 8-row swizzle atoms 1024 B apart.
+            constexpr uint64_t DESC_A = smem_desc(SMEM_LAYOUT_SW128, 16, 1024);
+            // B, MN-major: 128-byte chunks of N, B_CHUNK_BYTES apart; k rows 128 B apart, grouped by
+            // swizzle atom (8 rows = 1024 B for 16-bit operands, 4 rows = 512 B for 32-bit operands).
+            constexpr uint64_t DESC_B = (KIND == 0) ? smem_desc(SMEM_LAYOUT_SW128, Cfg::B_CHUNK_BYTES, 1024)
+                                                    : smem_desc(SMEM_LAYOUT_SW128_BASE32B, Cfg::B_CHUNK_BYTES, 512);
             constexpr uint32_t A_KSTEP = 32;                                          // UMMA_K elements along a 128 B row
             constexpr uint32_t B_KSTEP = Cfg::UMMA_K * 128;                           // UMMA_K rows of 128 B
             const uint32_t peer_empty = (CTAS == 2) ? map_to_cta(empty_bar, 1) : 0u;

@@ -252,14 +252,18 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // ---------------------------------------------------------------------------
 // descriptors
 // ---------------------------------------------------------------------------
-// Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes and
-// are stored without their 4 low bits.
+// Shared-memory matrix descriptor.  Offsets are in bytes and are stored without
+// their 4 low bits.
 //   bits  0-13 start address, 16-29 leading-dimension byte offset, 32-45 stride-
 //   dimension byte offset, 46-47 descriptor version (1 on sm_100), 61-63 swizzle
-//   mode (2 = 128 B).
-__host__ __device__ constexpr uint64_t smem_desc_sw128(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   mode: 2 = 128-byte swizzle of 16-byte units (8-row atoms, matches TMA SWIZZLE_128B),
+//         1 = 128-byte swizzle of 32-byte units (4-row atoms, matches TMA
+//             SWIZZLE_128B_ATOM_32B) -- the only layout an MN-major 32-bit operand may use.
+constexpr uint32_t SMEM_LAYOUT_SW128 = 2;
+constexpr uint32_t SMEM_LAYOUT_SW128_BASE32B = 1;
+__host__ __device__ constexpr uint64_t smem_desc(uint32_t layout, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return (uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32) |
-           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+           (uint64_t(1) << 46) | (uint64_t(layout) << 61);
 }
 __device__ __forceinline__ uint64_t smem_desc_at(uint64_t base, uint32_t smem_addr) {
     return base | uint64_t((smem_addr >> 4) & 0x3FFFu);
