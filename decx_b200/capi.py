@@ -33,6 +33,10 @@ def _load():
     lib.decxb200_gemm.argtypes = gemm_args
     lib.decxb200_gemm_ex.restype = ci
     lib.decxb200_gemm_ex.argtypes = gemm_args + [ci, ci]
+    lib.decxb200_gemm_host_arena_bytes.restype = sz
+    lib.decxb200_gemm_host_arena_bytes.argtypes = [ci, u32, u32, u32, ci]
+    lib.decxb200_gemm_host.restype = ci
+    lib.decxb200_gemm_host.argtypes = [ci, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
     lib.decxb200_last_launch_count.restype = ci
     lib.decxb200_last_launch_count.argtypes = []
     lib.decxb200_strerror.restype = ctypes.c_char_p
@@ -46,6 +50,7 @@ lib = _load()
 
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
+    "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
     "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
 ]
 

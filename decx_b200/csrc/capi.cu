@@ -140,11 +140,127 @@ size_t decxb200_gemm_workspace_bytes(int dtype, uint32_t M, uint32_t N, uint32_t
     return 0;
 }
 
-int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
-                     const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd,
-                     const void* alpha, const void* beta, void* workspace, size_t workspace_bytes, unsigned* status,
-                     int cta_group, int max_ctas) {
-    t_launches = 0;
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// internal building blocks shared by the device-pointer and the host-pointer entry points
+// ------------------------------------------------------------------------------------------
+namespace {
+
+struct Scalars {
+    float ar = 1.f, ai = 0.f, br = 0.f, bi = 0.f;
+};
+
+Scalars read_scalars(int dtype, const void* alpha, const void* beta) {
+    Scalars s;
+    if (alpha != nullptr) {
+        s.ar = static_cast<const float*>(alpha)[0];
+        if (dtype == DECXB200_CPLXF) s.ai = static_cast<const float*>(alpha)[1];
+    }
+    if (beta != nullptr) {
+        s.br = static_cast<const float*>(beta)[0];
+        if (dtype == DECXB200_CPLXF) s.bi = static_cast<const float*>(beta)[1];
+    }
+    return s;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline unsigned prepass_blocks(uint64_t work) {
+    const uint64_t b = work / 256 + 1;
+    return unsigned(b > 148ull * 16 ? 148ull * 16 : b);
+}
+
+// tf32 (hi, lo) planes of A.  complex: A is viewed as M x 2K floats with pitch 2*lda.
+int prep_a(cudaStream_t stream, bool cplx, const void* A, uint64_t lda, uint32_t M, uint32_t K, float* a_hi,
+           float* a_lo, uint64_t ldaw) {
+    const uint64_t ldx = cplx ? 2 * lda : lda;
+    const uint32_t Kr = cplx ? 2 * K : K;
+    const int vec = ((ldx % 4) == 0 && aligned16(A)) ? 1 : 0;
+    split_tf32_kernel<<<prepass_blocks(uint64_t(M) * ((Kr + 3) / 4)), 256, 0, stream>>>(
+        static_cast<const float*>(A), ldx, M, Kr, a_hi, a_lo, ldaw, vec);
+    ++t_launches;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+// tf32 (hi, lo) planes of B (complex: of its 2K x 2N real expansion).
+int prep_b(cudaStream_t stream, bool cplx, const void* B, uint64_t ldb, uint32_t K, uint32_t N, float* b_hi,
+           float* b_lo, uint64_t ldbw) {
+    if (!cplx) {
+        const int vec = ((ldb % 4) == 0 && aligned16(B)) ? 1 : 0;
+        split_tf32_kernel<<<prepass_blocks(uint64_t(K) * ((N + 3) / 4)), 256, 0, stream>>>(
+            static_cast<const float*>(B), ldb, K, N, b_hi, b_lo, ldbw, vec);
+    } else {
+        expand_split_cplx_b_kernel<<<prepass_blocks(uint64_t(K) * ((N + 1) / 2)), 256, 0, stream>>>(
+            static_cast<const float2*>(B), ldb, K, N, b_hi, b_lo, ldbw);
+    }
+    ++t_launches;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+void fill_common(GemmParams& p, const Scalars& sc, const void* C, void* D, unsigned* status) {
+    memset(&p, 0, sizeof(p));
+    p.D = D;
+    p.status = status;
+    p.wait_limit_ns = 4000000000ull;
+    p.alpha_re = sc.ar;
+    p.alpha_im = sc.ai;
+    p.beta_re = sc.br;
+    p.beta_im = sc.bi;
+    const bool use_c = (C != nullptr) && (sc.br != 0.f || sc.bi != 0.f);
+    p.C = use_c ? C : nullptr;
+}
+
+int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
+            const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc,
+            unsigned* status, int cta_group, int max_ctas) {
+    if ((lda % 8) != 0 || (ldb % 8) != 0 || !aligned16(A) || !aligned16(B)) return DECXB200_EALIGN;
+    GemmParams p;
+    fill_common(p, sc, C, D, status);
+    p.M = M; p.N = N; p.K = K;
+    p.ldd = ldd; p.ldc = ldc;
+    p.epi_mode = EPI_REAL;
+    p.vec_d = ((ldd % 8) == 0 && aligned16(D)) ? 1 : 0;
+    p.vec_c = (p.C != nullptr && (ldc % 8) == 0 && aligned16(C)) ? 1 : 0;
+    using C1 = GemmCfg<0, 1>;
+    CUtensorMap a0, b0;
+    int rc;
+    if ((rc = make_map(&a0, true, A, M, K, lda, C1::BK, C1::BM)) != 0) return rc;
+    if ((rc = make_map(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK)) != 0) return rc;
+    return cta_group == 1 ? launch_gemm<0, 1>(stream, dev, a0, a0, b0, b0, p, max_ctas)
+                          : launch_gemm<0, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
+}
+
+// M x Nr x Kr real 3xTF32 product of pre-split planes (complex: Nr = 2N, Kr = 2K; ldc/ldd in elements)
+int run_tf32(cudaStream_t stream, int dev, bool cplx, uint32_t M, uint32_t N, uint32_t K, const float* a_hi,
+             const float* a_lo, uint64_t ldaw, const float* b_hi, const float* b_lo, uint64_t ldbw, const void* C,
+             uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc, unsigned* status, int cta_group, int max_ctas) {
+    const uint32_t Kr = cplx ? 2 * K : K, Nr = cplx ? 2 * N : N;
+    GemmParams p;
+    fill_common(p, sc, C, D, status);
+    p.M = M; p.N = Nr; p.K = Kr;
+    p.ldd = cplx ? 2 * ldd : ldd;
+    p.ldc = cplx ? 2 * ldc : ldc;
+    p.epi_mode = cplx ? EPI_COMPLEX : EPI_REAL;
+    p.vec_d = ((p.ldd % 4) == 0 && aligned16(D)) ? 1 : 0;
+    p.vec_c = (p.C != nullptr && (p.ldc % 4) == 0 && aligned16(C)) ? 1 : 0;
+    using C1 = GemmCfg<1, 1>;
+    CUtensorMap a0, a1, b0, b1;
+    int rc;
+    if ((rc = make_map(&a0, false, a_hi, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
+    if ((rc = make_map(&a1, false, a_lo, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
+    if ((rc = make_map(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+        return rc;
+    if ((rc = make_map(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+        return rc;
+    return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
+                          : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);
+}
+
+int check_common(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, const void* B,
+                 uint64_t ldb, const void* C, uint64_t ldc, const void* D, uint64_t ldd, int& cta_group, int& dev) {
     if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF) return DECXB200_EINVAL;
     if (A == nullptr || B == nullptr || D == nullptr) return DECXB200_EINVAL;
     if (M == 0 || N == 0 || K == 0) return DECXB200_EINVAL;
@@ -153,57 +269,108 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
     if (cta_group != 1 && cta_group != 2) return DECXB200_EINVAL;
     if (dtype == DECXB200_CPLXF && (uint64_t(N) * 2 > 0xFFFFFFFFull || uint64_t(K) * 2 > 0xFFFFFFFFull))
         return DECXB200_ETOOLARGE;
-
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    int dev = 0;
-    cudaError_t ce = cudaGetDevice(&dev);
+    const cudaError_t ce = cudaGetDevice(&dev);
     if (ce != cudaSuccess) return int(ce);
     if (dev < 0 || dev >= MAX_DEVICES) return DECXB200_EINVAL;
+    return 0;
+}
 
-    GemmParams p;
-    memset(&p, 0, sizeof(p));
-    p.D = D;
-    p.status = status;
-    p.wait_limit_ns = 4000000000ull;
-    p.alpha_re = 1.f;
-    p.alpha_im = 0.f;
-    p.beta_re = 0.f;
-    p.beta_im = 0.f;
-    if (alpha != nullptr) {
-        p.alpha_re = static_cast<const float*>(alpha)[0];
-        if (dtype == DECXB200_CPLXF) p.alpha_im = static_cast<const float*>(alpha)[1];
-    }
-    if (beta != nullptr) {
-        p.beta_re = static_cast<const float*>(beta)[0];
-        if (dtype == DECXB200_CPLXF) p.beta_im = static_cast<const float*>(beta)[1];
-    }
-    const bool use_c = (C != nullptr) && (p.beta_re != 0.f || p.beta_im != 0.f);
-    p.C = use_c ? C : nullptr;
+inline uint64_t elem_size(int dtype) { return dtype == DECXB200_FP16 ? 2 : (dtype == DECXB200_FP32 ? 4 : 8); }
+// device row pitch (elements) of the staging copies: the reference's rule for device matrices, rows
+// rounded up to 128 bytes (srcs/modules/core/classes/GPU_Matrix.cu:35-61)
+inline uint64_t dev_pitch(int dtype, uint64_t width) { return round_up(width * elem_size(dtype), 128) / elem_size(dtype); }
 
-    CUtensorMap a0, a1, b0, b1;
-    int rc;
-    if (dtype == DECXB200_FP16) {
-        if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) != 0 ||
-            (reinterpret_cast<uintptr_t>(B) & 15) != 0)
-            return DECXB200_EALIGN;
-        p.M = M; p.N = N; p.K = K;
-        p.ldd = ldd; p.ldc = ldc;
-        p.epi_mode = EPI_REAL;
-        p.vec_d = ((ldd % 8) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) ? 1 : 0;
-        p.vec_c = (use_c && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
-        using C1 = GemmCfg<0, 1>;
-        if ((rc = make_map(&a0, true, A, M, K, lda, C1::BK, C1::BM)) != 0) return rc;
-        if ((rc = make_map(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK)) != 0) return rc;
-        a1 = a0;
-        b1 = b0;
-        return cta_group == 1 ? launch_gemm<0, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
-                              : launch_gemm<0, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);
+// streams and events of the host-pointer path, one set per device, created on first use
+struct HostPath {
+    bool ready = false;
+    cudaStream_t h2d = nullptr, comp = nullptr, d2h = nullptr;
+    cudaEvent_t ev_b = nullptr, ev_h2d[2] = {nullptr, nullptr}, ev_comp[2] = {nullptr, nullptr},
+                ev_d2h[2] = {nullptr, nullptr};
+};
+HostPath g_host[MAX_DEVICES];
+
+int host_path(int dev, HostPath*& hp) {
+    std::lock_guard<std::mutex> lk(g_dev_mutex);
+    hp = &g_host[dev];
+    if (hp->ready) return 0;
+    cudaError_t e;
+    if ((e = cudaStreamCreateWithFlags(&hp->h2d, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+    if ((e = cudaStreamCreateWithFlags(&hp->comp, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+    if ((e = cudaStreamCreateWithFlags(&hp->d2h, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+    cudaEvent_t* evs[] = {&hp->ev_b, &hp->ev_h2d[0], &hp->ev_h2d[1], &hp->ev_comp[0], &hp->ev_comp[1],
+                          &hp->ev_d2h[0], &hp->ev_d2h[1]};
+    for (cudaEvent_t* ev : evs)
+        if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess) return int(e);
+    hp->ready = true;
+    return 0;
+}
+
+// rows of A / D handled per pipeline step of the host-pointer path
+uint32_t host_block_rows(uint32_t M) {
+    if (M <= 2048) return M;
+    uint32_t rb = uint32_t(round_up((uint64_t(M) + 7) / 8, 256));   // about 8 steps, whole 256-row tiles
+    if (rb < 1024) rb = 1024;
+    return rb > M ? M : rb;
+}
+
+struct HostArena {
+    uint64_t b_dev, b_hi, b_lo, a_dev[2], a_hi[2], a_lo[2], c_dev[2], d_dev[2], total;
+    uint64_t ldb_d, lda_d, ldcd_d, ldaw, ldbw;
+    uint32_t rb;
+};
+
+HostArena plan_arena(int dtype, uint32_t M, uint32_t N, uint32_t K, bool has_c) {
+    HostArena a;
+    memset(&a, 0, sizeof(a));
+    const uint64_t es = elem_size(dtype);
+    const bool cplx = dtype == DECXB200_CPLXF, split = dtype != DECXB200_FP16;
+    a.rb = host_block_rows(M);
+    a.ldb_d = dev_pitch(dtype, N);
+    a.lda_d = dev_pitch(dtype, K);
+    a.ldcd_d = dev_pitch(dtype, N);
+    a.ldaw = round_up(cplx ? 2ull * K : K, 32);
+    a.ldbw = round_up(cplx ? 2ull * N : N, 32);
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { const uint64_t o = off; off += round_up(bytes, 256); return o; };
+    a.b_dev = take(uint64_t(K) * a.ldb_d * es);
+    if (split) {
+        const uint64_t kb = (cplx ? 2ull * K : K) * a.ldbw * 4;
+        a.b_hi = take(kb);
+        a.b_lo = take(kb);
     }
+    for (int i = 0; i < 2; ++i) {
+        a.a_dev[i] = take(uint64_t(a.rb) * a.lda_d * es);
+        if (split) {
+            a.a_hi[i] = take(uint64_t(a.rb) * a.ldaw * 4);
+            a.a_lo[i] = take(uint64_t(a.rb) * a.ldaw * 4);
+        }
+        if (has_c) a.c_dev[i] = take(uint64_t(a.rb) * a.ldcd_d * es);
+        a.d_dev[i] = take(uint64_t(a.rb) * a.ldcd_d * es);
+    }
+    a.total = off;
+    return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
+                     const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                     const void* alpha, const void* beta, void* workspace, size_t workspace_bytes, unsigned* status,
+                     int cta_group, int max_ctas) {
+    t_launches = 0;
+    int dev = 0;
+    int rc = check_common(dtype, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, cta_group, dev);
+    if (rc != 0) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const Scalars sc = read_scalars(dtype, alpha, beta);
+    if (dtype == DECXB200_FP16)
+        return run_f16(stream, dev, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, sc, status, cta_group, max_ctas);
 
     // fp32 / cplxf: tf32 (hi, lo) planes in the workspace, then one real 3xTF32 GEMM
     const bool cplx = (dtype == DECXB200_CPLXF);
-    const uint32_t Kr = cplx ? 2 * K : K;      // real extents seen by the MMA
-    const uint32_t Nr = cplx ? 2 * N : N;
+    const uint32_t Kr = cplx ? 2 * K : K, Nr = cplx ? 2 * N : N;
     const size_t need = decxb200_gemm_workspace_bytes(dtype, M, N, K);
     if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
         return DECXB200_EWORKSPACE;
@@ -215,45 +382,99 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
     float* a_lo = reinterpret_cast<float*>(w + a_bytes);
     float* b_hi = reinterpret_cast<float*>(w + 2 * a_bytes);
     float* b_lo = reinterpret_cast<float*>(w + 2 * a_bytes + b_bytes);
+    if ((rc = prep_a(stream, cplx, A, lda, M, K, a_hi, a_lo, ldaw)) != 0) return rc;
+    if ((rc = prep_b(stream, cplx, B, ldb, K, N, b_hi, b_lo, ldbw)) != 0) return rc;
+    return run_tf32(stream, dev, cplx, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, C, ldc, D, ldd, sc, status,
+                    cta_group, max_ctas);
+}
 
-    {
-        // A (complex: viewed as M x 2K floats with pitch 2*lda)
-        const uint64_t ldx = cplx ? 2 * lda : lda;
-        const int vec = ((ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0) ? 1 : 0;
-        const uint64_t work = uint64_t(M) * ((Kr + 3) / 4);
-        const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 16 ? 148ull * 16 : work / 256 + 1);
-        split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(A), ldx, M, Kr, a_hi, a_lo, ldaw, vec);
-        ++t_launches;
-    }
-    if (!cplx) {
-        const int vec = ((ldb % 4) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0) ? 1 : 0;
-        const uint64_t work = uint64_t(K) * ((N + 3) / 4);
-        const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 16 ? 148ull * 16 : work / 256 + 1);
-        split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(B), ldb, K, N, b_hi, b_lo, ldbw, vec);
-        ++t_launches;
-    } else {
-        const uint64_t work = uint64_t(K) * ((N + 1) / 2);
-        const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 16 ? 148ull * 16 : work / 256 + 1);
-        expand_split_cplx_b_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float2*>(B), ldb, K, N, b_hi, b_lo,
-                                                               ldbw);
-        ++t_launches;
-    }
-    ce = cudaGetLastError();
-    if (ce != cudaSuccess) return int(ce);
+size_t decxb200_gemm_host_arena_bytes(int dtype, uint32_t M, uint32_t N, uint32_t K, int has_c) {
+    if (M == 0 || N == 0 || K == 0) return 0;
+    if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF) return 0;
+    return size_t(plan_arena(dtype, M, N, K, has_c != 0).total);
+}
 
-    p.M = M; p.N = Nr; p.K = Kr;
-    p.ldd = cplx ? 2 * ldd : ldd;
-    p.ldc = cplx ? 2 * ldc : ldc;
-    p.epi_mode = cplx ? EPI_COMPLEX : EPI_REAL;
-    p.vec_d = ((p.ldd % 4) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) ? 1 : 0;
-    p.vec_c = (use_c && (p.ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
-    using C1 = GemmCfg<1, 1>;
-    if ((rc = make_map(&a0, false, a_hi, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
-    if ((rc = make_map(&a1, false, a_lo, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
-    if ((rc = make_map(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0) return rc;
-    if ((rc = make_map(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0) return rc;
-    return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
-                          : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);
+int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, const void* B,
+                       uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd, const void* alpha,
+                       const void* beta, void* arena, size_t arena_bytes, unsigned* status) {
+    t_launches = 0;
+    int dev = 0, cta_group = 0;
+    int rc = check_common(dtype, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, cta_group, dev);
+    if (rc != 0) return rc;
+    const Scalars sc = read_scalars(dtype, alpha, beta);
+    const bool use_c = (C != nullptr) && (sc.br != 0.f || sc.bi != 0.f);
+    const HostArena ar = plan_arena(dtype, M, N, K, use_c);
+    if (arena == nullptr || arena_bytes < ar.total || (reinterpret_cast<uintptr_t>(arena) & 255) != 0)
+        return DECXB200_EWORKSPACE;
+    HostPath* hp = nullptr;
+    if ((rc = host_path(dev, hp)) != 0) return rc;
+
+    const uint64_t es = elem_size(dtype);
+    const bool cplx = dtype == DECXB200_CPLXF, split = dtype != DECXB200_FP16;
+    uint8_t* base = static_cast<uint8_t*>(arena);
+    auto at = [&](uint64_t off) { return base + off; };
+    cudaError_t e;
+#define DXB_CUDA(call) do { e = (call); if (e != cudaSuccess) { cudaDeviceSynchronize(); return int(e); } } while (0)
+
+    // B: one copy, one split; every row block of A reuses it
+    DXB_CUDA(cudaMemcpy2DAsync(at(ar.b_dev), ar.ldb_d * es, B, ldb * es, uint64_t(N) * es, K, cudaMemcpyHostToDevice,
+                               hp->h2d));
+    DXB_CUDA(cudaEventRecord(hp->ev_b, hp->h2d));
+    DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_b, 0));
+    if (split) {
+        rc = prep_b(hp->comp, cplx, at(ar.b_dev), ar.ldb_d, K, N, reinterpret_cast<float*>(at(ar.b_hi)),
+                    reinterpret_cast<float*>(at(ar.b_lo)), ar.ldbw);
+        if (rc != 0) { cudaDeviceSynchronize(); return rc; }
+    }
+    // row blocks: H2D of block i+1 and D2H of block i-1 overlap the GEMM of block i
+    uint32_t step = 0;
+    for (uint32_t r0 = 0; r0 < M; r0 += ar.rb, ++step) {
+        const uint32_t rows = (M - r0 < ar.rb) ? M - r0 : ar.rb;
+        const int b = int(step & 1u);
+        const uint8_t* a_src = static_cast<const uint8_t*>(A) + uint64_t(r0) * lda * es;
+        if (step >= 2) DXB_CUDA(cudaStreamWaitEvent(hp->h2d, hp->ev_comp[b], 0));   // staging buffers free again
+        DXB_CUDA(cudaMemcpy2DAsync(at(ar.a_dev[b]), ar.lda_d * es, a_src, lda * es, uint64_t(K) * es, rows,
+                                   cudaMemcpyHostToDevice, hp->h2d));
+        if (use_c) {
+            const uint8_t* c_src = static_cast<const uint8_t*>(C) + uint64_t(r0) * ldc * es;
+            DXB_CUDA(cudaMemcpy2DAsync(at(ar.c_dev[b]), ar.ldcd_d * es, c_src, ldc * es, uint64_t(N) * es, rows,
+                                       cudaMemcpyHostToDevice, hp->h2d));
+        }
+        DXB_CUDA(cudaEventRecord(hp->ev_h2d[b], hp->h2d));
+        DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_h2d[b], 0));
+        if (step >= 2) DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_d2h[b], 0));  // D staging buffer drained
+        const void* c_dev = use_c ? at(ar.c_dev[b]) : nullptr;
+        if (!split) {
+            rc = run_f16(hp->comp, dev, rows, N, K, at(ar.a_dev[b]), ar.lda_d, at(ar.b_dev), ar.ldb_d, c_dev,
+                         ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, sc, status, cta_group, 0);
+        } else {
+            float* a_hi = reinterpret_cast<float*>(at(ar.a_hi[b]));
+            float* a_lo = reinterpret_cast<float*>(at(ar.a_lo[b]));
+            rc = prep_a(hp->comp, cplx, at(ar.a_dev[b]), ar.lda_d, rows, K, a_hi, a_lo, ar.ldaw);
+            if (rc == 0)
+                rc = run_tf32(hp->comp, dev, cplx, rows, N, K, a_hi, a_lo, ar.ldaw,
+                              reinterpret_cast<float*>(at(ar.b_hi)), reinterpret_cast<float*>(at(ar.b_lo)), ar.ldbw,
+                              c_dev, ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, sc, status, cta_group, 0);
+        }
+        if (rc != 0) { cudaDeviceSynchronize(); return rc; }
+        DXB_CUDA(cudaEventRecord(hp->ev_comp[b], hp->comp));
+        DXB_CUDA(cudaStreamWaitEvent(hp->d2h, hp->ev_comp[b], 0));
+        uint8_t* d_dst = static_cast<uint8_t*>(D) + uint64_t(r0) * ldd * es;
+        DXB_CUDA(cudaMemcpy2DAsync(d_dst, ldd * es, at(ar.d_dev[b]), ar.ldcd_d * es, uint64_t(N) * es, rows,
+                                   cudaMemcpyDeviceToHost, hp->d2h));
+        DXB_CUDA(cudaEventRecord(hp->ev_d2h[b], hp->d2h));
+    }
+    DXB_CUDA(cudaStreamSynchronize(hp->d2h));
+    DXB_CUDA(cudaStreamSynchronize(hp->comp));
+    DXB_CUDA(cudaStreamSynchronize(hp->h2d));
+#undef DXB_CUDA
+    if (status != nullptr) {
+        unsigned st = 0;
+        e = cudaMemcpy(&st, status, sizeof(st), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return int(e);
+        if (st != 0) return DECXB200_EKERNEL;
+    }
+    return 0;
 }
 
 int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,

@@ -66,3 +66,44 @@ def gemm(A, B, C=None, alpha=None, beta=None, out=None, workspace=None, status=N
             status.data_ptr() if status is not None else None, cta_group, max_ctas)
     capi.check(code)
     return out
+
+
+def host_arena_bytes(dtype, M, N, K, has_c=False):
+    return int(capi.lib.decxb200_gemm_host_arena_bytes(_DTYPES[dtype], M, N, K, int(bool(has_c))))
+
+
+def gemm_host(A, B, C=None, alpha=None, beta=None, out=None, arena=None, status=None, device=None):
+    """Host-matrix form: A, B, C, out are CPU tensors (pin them for full PCIe speed).
+
+    Synchronous; copies, pre-passes and GEMM are pipelined inside the library
+    (``decxb200_gemm_host``).  ``arena`` is device scratch (uint8 CUDA tensor); it is allocated
+    here when missing or too small.  Returns ``out``.
+    """
+    if A.is_cuda or B.is_cuda:
+        raise RuntimeError("gemm_host takes host tensors; use gemm() for device tensors")
+    if not torch.cuda.is_available():
+        raise RuntimeError("decx_b200 needs a CUDA device (no CPU fallback)")
+    dt = _DTYPES.get(A.dtype)
+    if dt is None or B.dtype != A.dtype or (C is not None and C.dtype != A.dtype):
+        raise TypeError("A, B, C must share one dtype out of float16, float32, complex64")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"A is {M}x{K} but B is {K2}x{N}")
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype).pin_memory()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _a, pa = _scalar(dt, alpha)
+    _b, pb = _scalar(dt, beta if C is not None else None)
+    use_c = C is not None and beta is not None and complex(beta) != 0
+    need = int(capi.lib.decxb200_gemm_host_arena_bytes(dt, M, N, K, int(use_c)))
+    if arena is None or arena.numel() < need:
+        arena = torch.empty(need, dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        code = capi.lib.decxb200_gemm_host(
+            dt, M, N, K, A.data_ptr(), _ld(A), B.data_ptr(), _ld(B),
+            C.data_ptr() if C is not None else None, _ld(C) if C is not None else 0,
+            out.data_ptr(), _ld(out), pa, pb, arena.data_ptr(), need,
+            status.data_ptr() if status is not None else None)
+    capi.check(code)
+    return out

@@ -86,6 +86,30 @@ DECXB200_API int decxb200_gemm_ex(int dtype, void* stream, uint32_t M, uint32_t 
                                   void* workspace, size_t workspace_bytes, unsigned* status,
                                   int cta_group, int max_ctas);
 
+/*
+ * Host-pointer form: A, B, C, D are HOST matrices (pinned memory gives full PCIe speed,
+ * pageable memory works).  The call copies B once, then walks A and D in row blocks so that
+ * the host->device copy of block i+1 and the device->host copy of block i-1 overlap the GEMM
+ * of block i, on three library-owned streams of the current device.  It returns when D is
+ * complete in host memory.
+ *
+ *   arena: DEVICE scratch of at least decxb200_gemm_host_arena_bytes(), 256-byte aligned.
+ *          The library allocates no device memory itself: DECX's device memory pool (or any
+ *          other allocator of the caller) provides it.
+ *   has_c: whether a C operand with beta != 0 will be passed.
+ *
+ * This is the backend of the host-matrix overloads de::blas::cuda::GEMM(de::Matrix&, ...)
+ * that the reference declares in srcs/includes/DECX/BLAS/BLAS.h:69-70 and never defines; it
+ * covers what de::Memcpy (srcs/modules/core/data transmission/data_transmission.cu:105-180,
+ * cudaMemcpy2DAsync honouring both pitches) plus the device GEMM plus de::Memcpy back would do.
+ */
+DECXB200_API size_t decxb200_gemm_host_arena_bytes(int dtype, uint32_t M, uint32_t N, uint32_t K, int has_c);
+DECXB200_API int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K,
+                                    const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                                    const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                                    const void* alpha, const void* beta,
+                                    void* arena, size_t arena_bytes, unsigned* status);
+
 /* Number of kernels the last decxb200_gemm* call of this thread launched (pre-passes included). */
 DECXB200_API int decxb200_last_launch_count(void);
 

@@ -1,0 +1,157 @@
+"""numpy front end of oracle/gemm_oracle.c and of the reference build in oracle/_ref/.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by the
+cpu_baseline / reference legs of bench.py -- never by the product package.
+"""
+import ctypes
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "liboracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libdecx_ref_cpu.so")
+
+FP32, FP16, CPLXF = 1, 3, 5
+
+
+def build(ref_root="/root/reference"):
+    """Compile the C restatement; compile the reference's CPU GEMM too when its sources are present."""
+    subprocess.run(["make", "-C", HERE, "liboracle.so"], check=True, stdout=subprocess.DEVNULL)
+    if os.path.isdir(os.path.join(ref_root, "srcs")):
+        subprocess.run(["make", "-C", HERE, "ref", f"REF={ref_root}"], check=True, stdout=subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        L = ctypes.CDLL(ORACLE_SO)
+        u32, sz, vp, d, f = ctypes.c_uint32, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_double, ctypes.c_float
+        L.oracle_gemm_f32.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, d, d, vp, sz]
+        L.oracle_gemm_c32.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, vp, vp, vp, sz]
+        L.oracle_gemm_f16.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, f, f, vp, sz]
+        L.oracle_metric.restype = d
+        L.oracle_metric.argtypes = [u32, u32, ctypes.c_int, vp, sz, vp, sz, vp, vp]
+        L.oracle_norms_f32.argtypes = [u32, u32, u32, ctypes.c_int, vp, sz, vp, sz, vp, vp]
+        L.oracle_half_to_float.argtypes = [vp, vp, sz]
+        L.oracle_float_to_half.argtypes = [vp, vp, sz]
+        L.oracle_set_threads.argtypes = [ctypes.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def _c(a, dt):
+    return None if a is None else np.ascontiguousarray(a, dtype=dt)
+
+
+def gemm(A, B, C=None, alpha=1.0, beta=0.0):
+    """Oracle result of D = alpha*A@B + beta*C.
+
+    float32 -> float64 result; complex64 -> complex128 result; float16 -> float32 result
+    (fp32 accumulation; the caller rounds with ``to_half`` for the stored fp16 value).
+    """
+    L = lib()
+    M, K = A.shape
+    K2, N = B.shape
+    assert K == K2
+    if A.dtype == np.float32:
+        A, B, C = _c(A, np.float32), _c(B, np.float32), _c(C, np.float32)
+        D = np.empty((M, N), dtype=np.float64)
+        L.oracle_gemm_f32(M, N, K, _p(A), K, _p(B), N, _p(C), N, float(alpha), float(beta), _p(D), N)
+        return D
+    if A.dtype == np.complex64:
+        A, B, C = _c(A, np.complex64), _c(B, np.complex64), _c(C, np.complex64)
+        D = np.empty((M, N), dtype=np.complex128)
+        al = np.array([complex(alpha).real, complex(alpha).imag], dtype=np.float64)
+        be = np.array([complex(beta).real, complex(beta).imag], dtype=np.float64)
+        L.oracle_gemm_c32(M, N, K, _p(A), K, _p(B), N, _p(C), N, _p(al), _p(be), _p(D), N)
+        return D
+    if A.dtype == np.float16:
+        A, B, C = _c(A, np.float16), _c(B, np.float16), _c(C, np.float16)
+        D = np.empty((M, N), dtype=np.float32)
+        L.oracle_gemm_f16(M, N, K, _p(A), K, _p(B), N, _p(C), N, float(alpha), float(beta), _p(D), N)
+        return D
+    raise TypeError(A.dtype)
+
+
+def to_half(x):
+    """fp32 -> fp16 with the oracle's own round-to-nearest-even conversion."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.float16)
+    lib().oracle_float_to_half(_p(x), _p(out), x.size)
+    return out
+
+
+def metric(D, Dref, A, B):
+    """max_ij |D - Dref| / (||A_i,:|| * ||B_:,j||), the parity metric of this path."""
+    L = lib()
+    M, K = A.shape
+    N = B.shape[1]
+    cplx = int(np.iscomplexobj(A))
+    Af = np.ascontiguousarray(A.astype(np.complex64 if cplx else np.float32))
+    Bf = np.ascontiguousarray(B.astype(np.complex64 if cplx else np.float32))
+    rn = np.empty(M, dtype=np.float64)
+    cn = np.empty(N, dtype=np.float64)
+    L.oracle_norms_f32(M, N, K, cplx, _p(Af), K, _p(Bf), N, _p(rn), _p(cn))
+    wide = np.complex128 if cplx else np.float64
+    Dw = np.ascontiguousarray(D.astype(wide))
+    Rw = np.ascontiguousarray(Dref.astype(wide))
+    return float(L.oracle_metric(M, N, cplx, _p(Dw), N, _p(Rw), N, _p(rn), _p(cn)))
+
+
+# ------------------------------------------------------------------ reference build (oracle/_ref)
+def ref_available():
+    return os.path.exists(REF_SO)
+
+
+_REF_CHILD = r"""
+import ctypes, json, sys
+import numpy as np
+so, dtype, threads, repeats, fin, fout = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5], sys.argv[6]
+L = ctypes.CDLL(so)
+L.decx_ref_max_threads.restype = ctypes.c_uint
+z = np.load(fin)
+A, B = np.ascontiguousarray(z["A"]), np.ascontiguousarray(z["B"])
+M, K = A.shape; N = B.shape[1]
+D = np.zeros((M, N), dtype=A.dtype)
+times = np.zeros(repeats, dtype=np.float64)
+threads = min(threads, int(L.decx_ref_max_threads()))
+vp = ctypes.c_void_p
+L.decx_ref_cpu_gemm.argtypes = [ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, vp, ctypes.c_size_t, vp,
+                                ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_uint, ctypes.c_int, vp]
+rc = L.decx_ref_cpu_gemm(dtype, M, N, K, A.ctypes.data, K, B.ctypes.data, N, D.ctypes.data, N, threads, repeats,
+                         times.ctypes.data)
+np.savez(fout, D=D, times=times, threads=np.array([threads]), rc=np.array([rc]))
+"""
+
+
+def ref_cpu_gemm(A, B, threads=8, repeats=1, tmpdir=None):
+    """Run the reference's de::blas::cpu::GEMM on (A, B) in a child process (one shape per process).
+
+    Returns (D, per-call seconds, threads used).  float32 and complex64 only, plain A@B only.
+    """
+    import tempfile
+    if not ref_available():
+        raise RuntimeError("oracle/_ref/libdecx_ref_cpu.so has not been built")
+    dt = FP32 if A.dtype == np.float32 else CPLXF
+    with tempfile.TemporaryDirectory(dir=tmpdir) as td:
+        fin, fout = os.path.join(td, "in.npz"), os.path.join(td, "out.npz")
+        np.savez(fin, A=A, B=B)
+        subprocess.run([sys.executable, "-c", _REF_CHILD, REF_SO, str(dt), str(threads), str(repeats), fin, fout],
+                       check=True)
+        z = np.load(fout)
+        if int(z["rc"][0]) != 0:
+            raise RuntimeError("reference harness rejected the call")
+        return z["D"], z["times"], int(z["threads"][0])

@@ -1,0 +1,60 @@
+"""CPU tests of the C-ABI library: it loads without a GPU, exports every symbol the header
+declares, and rejects bad arguments before touching CUDA."""
+import ctypes
+import os
+import re
+
+from decx_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            names |= set(re.findall(r"DECXB200_API[^;(]*?\b(decxb200_\w+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    declared = _declared()
+    assert declared, "no declarations found in include/*.h"
+    for name in sorted(declared):
+        assert hasattr(capi.lib, name), f"{name} is declared in include/ but not exported"
+    assert declared == set(capi.EXPORTS), "decx_b200/capi.py and include/decx_b200.h disagree"
+
+
+def test_version_and_strerror():
+    assert capi.lib.decxb200_version().decode().count(".") == 1
+    assert capi.lib.decxb200_strerror(0) == b"success"
+    for code in (-1, -2, -3, -4, -5, -6):
+        assert len(capi.lib.decxb200_strerror(code)) > 10
+
+
+def test_workspace_sizes():
+    ws = capi.workspace_bytes
+    assert ws(capi.FP16, 4096, 4096, 4096) == 0
+    # fp32: (hi, lo) planes of A (M x K) and B (K x N), rows padded to 32 floats
+    assert ws(capi.FP32, 8192, 8192, 8192) == 4 * 8192 * 8192 * 4
+    assert ws(capi.FP32, 5, 3, 7) == 2 * 768 + 2 * 1024   # 640- and 896-byte planes padded to 256 B
+    # cplxf: A viewed as M x 2K floats, B expanded to 2K x 2N floats
+    assert ws(capi.CPLXF, 4096, 4096, 4096) == 2 * 4096 * 8192 * 4 + 2 * 8192 * 8192 * 4
+    assert ws(capi.FP32, 0, 4, 4) == 0
+    assert capi.lib.decxb200_gemm_host_arena_bytes(capi.FP16, 0, 1, 1, 0) == 0
+    assert capi.lib.decxb200_gemm_host_arena_bytes(capi.FP16, 4096, 4096, 4096, 0) > 3 * 4096 * 4096 * 2 // 2
+
+
+def test_bad_arguments_are_rejected_without_a_gpu():
+    g = capi.lib.decxb200_gemm
+    buf = (ctypes.c_float * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    args = lambda dt, M, N, K, A, B, D, lda=8, ldb=8, ldd=8: (dt, None, M, N, K, A, lda, B, ldb, None, 0, D, ldd,
+                                                              None, None, None, 0, None)
+    assert g(*args(2, 4, 4, 4, p, p, p)) == -1            # unknown dtype
+    assert g(*args(capi.FP32, 0, 4, 4, p, p, p)) == -1    # zero extent
+    assert g(*args(capi.FP32, 4, 4, 4, None, p, p)) == -1  # null operand
+    assert g(*args(capi.FP32, 4, 4, 4, p, p, p, lda=3)) == -1  # pitch smaller than width
+    assert capi.lib.decxb200_gemm_ex(*args(capi.FP32, 4, 4, 4, p, p, p), 3, 0) == -1  # bad cta_group
