@@ -9,8 +9,16 @@
 //   warp 0      TMA producer: 128-byte-swizzled tiles of A (K-major) and of row-major
 //               B (consumed MN-major, so B is never transposed) into a ring of stages
 //   warp 1      allocates TMEM and issues tcgen05.mma; fp32 accumulators live in TMEM,
-//               two of them, so the epilogue of tile i overlaps the main loop of i+1
-//   warps 2..5  epilogue: tcgen05.ld -> alpha/beta/C -> global stores (predicated edges)
+//               two of them, so draining one overlaps the MMAs into the other
+//   warps 2..   epilogue: tcgen05.ld -> alpha/beta/C -> global stores (predicated edges)
+//
+// Accumulation chains.  The tensor core adds into its fp32 accumulator with truncation, so a
+// long chain of same-signed terms drifts by about (chain length) * 2^-24 relative -- 4e-6 at
+// K = 1000 on all-positive data, beyond fp32 behaviour.  The 3xTF32 kernel therefore
+// accumulates in TMEM only over chunks of CHUNK_KB k-blocks (K = 128); its eight epilogue
+// warps add every finished chunk into fp32 registers (round to nearest) while the MMAs of
+// the next chunk run into the other TMEM accumulator.  The fp16 kernel keeps one chain per
+// tile: its output precision (2^-11) is far coarser than the drift.
 //
 // KIND 0  fp16 operands, kind::f16, fp16 output.
 // KIND 1  fp32 operands pre-split into tf32 (hi, lo) planes, kind::tf32, three MMAs per
@@ -74,7 +82,11 @@ struct GemmCfg {
     static constexpr int STAGE = NPL * (A_TILE + B_TILE);
     static constexpr int STAGES = (192 * 1024) / STAGE;
     static constexpr int TMEM_COLS = 512;                 // two 256-column accumulators
-    static constexpr int THREADS = 192;
+    static constexpr bool PROMOTE = (KIND == 1);          // chunked TMEM chains summed in registers
+    static constexpr int CHUNK_KB = 4;                    // k-blocks per TMEM chain when PROMOTE
+    static constexpr int EPI_WARPS = PROMOTE ? 8 : 4;
+    static constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // accumulator columns per epilogue thread
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int SMEM_BYTES = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
 };
@@ -96,12 +108,9 @@ __device__ __forceinline__ void report(const GemmParams& p, unsigned code) {
 }
 
 template <int KIND>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, const uint32_t (&v)[32]) {
-    // v holds the fp32 accumulators of columns col0 .. col0+31 of `row`
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, float (&acc)[32]) {
+    // acc holds the fp32 accumulators of columns col0 .. col0+31 of `row` (clobbered)
     const bool has_c = (p.C != nullptr);
-    float acc[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(v[i]);
     const uint32_t ncols = min(32u, p.N - col0);
 
     if constexpr (KIND == 0) {
@@ -202,7 +211,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
 }
 
 template <int KIND, int CTAS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                     const GemmParams p) {
@@ -230,6 +239,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const uint32_t n_tiles = p.tiles_m * p.tiles_n;
     const uint32_t n_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
     const uint64_t limit = p.wait_limit_ns;
+    // k-blocks per TMEM accumulation chain: a few when the epilogue sums chunks in registers, else all
+    const uint32_t chunk_kb = Cfg::PROMOTE ? uint32_t(Cfg::CHUNK_KB) : n_kb;
+    const uint32_t n_chunks = (n_kb + chunk_kb - 1) / chunk_kb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -238,7 +250,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(accf_bar + 8 * a, 1);
-            mbar_init(acce_bar + 8 * a, 4 * CTAS);
+            mbar_init(acce_bar + 8 * a, Cfg::EPI_WARPS * CTAS);
         }
         fence_mbar_init();
     }
@@ -319,50 +331,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             constexpr uint32_t B_KSTEP = Cfg::UMMA_K * 128;                           // UMMA_K rows of 128 B
             const uint32_t peer_empty = (CTAS == 2) ? map_to_cta(empty_bar, 1) : 0u;
             const uint32_t peer_accf = (CTAS == 2) ? map_to_cta(accf_bar, 1) : 0u;
-            uint32_t s = 0, ph = 0, it = 0;
+            uint32_t s = 0, ph = 0, it = 0;          // `it` counts accumulation chains (chunks)
             bool ok = true;
-            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++it) {
-                const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
-                if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
-                    report(p, KS_TIMEOUT_MMA_ACC);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + a * Cfg::BN;
-                for (uint32_t kb = 0; kb < n_kb; ++kb) {
-                    if (!mbar_wait_bounded(full_bar + 8 * s, ph, limit)) {
-                        report(p, KS_TIMEOUT_MMA_FULL);
+            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
+                for (uint32_t c = 0; c < n_chunks && ok; ++c, ++it) {
+                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                    if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
+                        report(p, KS_TIMEOUT_MMA_ACC);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t stage = smem_base + s * Cfg::STAGE;
-                    const uint32_t a0 = stage, b0 = stage + Cfg::NPL * Cfg::A_TILE;
-#pragma unroll
-                    for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
-                        const uint32_t acc_flag = (kb | uint32_t(k)) ? 1u : 0u;
-                        if constexpr (KIND == 0) {
-                            umma_ss<0, CTAS>(d_tmem, smem_desc_at(DESC_A, a0 + k * A_KSTEP),
-                                             smem_desc_at(DESC_B, b0 + k * B_KSTEP), Cfg::IDESC, acc_flag);
-                        } else {
-                            const uint64_t a_hi = smem_desc_at(DESC_A, a0 + k * A_KSTEP);
-                            const uint64_t a_lo = smem_desc_at(DESC_A, a0 + Cfg::A_TILE + k * A_KSTEP);
-                            const uint64_t b_hi = smem_desc_at(DESC_B, b0 + k * B_KSTEP);
-                            const uint64_t b_lo = smem_desc_at(DESC_B, b0 + Cfg::B_TILE + k * B_KSTEP);
-                            // small terms first, the dominant hi*hi product last
-                            umma_ss<1, CTAS>(d_tmem, a_lo, b_hi, Cfg::IDESC, acc_flag);
-                            umma_ss<1, CTAS>(d_tmem, a_hi, b_lo, Cfg::IDESC, 1u);
-                            umma_ss<1, CTAS>(d_tmem, a_hi, b_hi, Cfg::IDESC, 1u);
+                    const uint32_t d_tmem = tmem_base + a * Cfg::BN;
+                    const uint32_t kb_end = min(n_kb, (c + 1) * chunk_kb);
+                    for (uint32_t kb = c * chunk_kb; kb < kb_end; ++kb) {
+                        if (!mbar_wait_bounded(full_bar + 8 * s, ph, limit)) {
+                            report(p, KS_TIMEOUT_MMA_FULL);
+                            ok = false;
+                            break;
                         }
+                        tc_fence_after_sync();
+                        const uint32_t stage = smem_base + s * Cfg::STAGE;
+                        const uint32_t a0 = stage, b0 = stage + Cfg::NPL * Cfg::A_TILE;
+#pragma unroll
+                        for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
+                            const uint32_t acc_flag = ((kb - c * chunk_kb) | uint32_t(k)) ? 1u : 0u;
+                            if constexpr (KIND == 0) {
+                                umma_ss<0, CTAS>(d_tmem, smem_desc_at(DESC_A, a0 + k * A_KSTEP),
+                                                 smem_desc_at(DESC_B, b0 + k * B_KSTEP), Cfg::IDESC, acc_flag);
+                            } else {
+                                const uint64_t a_hi = smem_desc_at(DESC_A, a0 + k * A_KSTEP);
+                                const uint64_t a_lo = smem_desc_at(DESC_A, a0 + Cfg::A_TILE + k * A_KSTEP);
+                                const uint64_t b_hi = smem_desc_at(DESC_B, b0 + k * B_KSTEP);
+                                const uint64_t b_lo = smem_desc_at(DESC_B, b0 + Cfg::B_TILE + k * B_KSTEP);
+                                // small terms first, the dominant hi*hi product last
+                                umma_ss<1, CTAS>(d_tmem, a_lo, b_hi, Cfg::IDESC, acc_flag);
+                                umma_ss<1, CTAS>(d_tmem, a_hi, b_lo, Cfg::IDESC, 1u);
+                                umma_ss<1, CTAS>(d_tmem, a_hi, b_hi, Cfg::IDESC, 1u);
+                            }
+                        }
+                        umma_commit<CTAS>(empty_bar + 8 * s);             // stage free once these MMAs retire
+                        if constexpr (CTAS == 2) umma_commit<CTAS>(peer_empty + 8 * s);
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
-                    umma_commit<CTAS>(empty_bar + 8 * s);                 // stage free once these MMAs retire
-                    if constexpr (CTAS == 2) umma_commit<CTAS>(peer_empty + 8 * s);
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
-                }
-                if (ok) {
-                    umma_commit<CTAS>(accf_bar + 8 * a);                  // accumulator complete
-                    if constexpr (CTAS == 2) umma_commit<CTAS>(peer_accf + 8 * a);
+                    if (ok) {
+                        umma_commit<CTAS>(accf_bar + 8 * a);              // chain complete
+                        if constexpr (CTAS == 2) umma_commit<CTAS>(peer_accf + 8 * a);
+                    }
                 }
             }
             // tail: both accumulators drained by every epilogue warp (of both CTAs)
@@ -377,38 +392,87 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------------ epilogue (warps 2..)
         const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
+        const uint32_t colpart = (warp - 2u) >> 2;           // which EPI_COLS-wide slice of the 256 columns
         const uint32_t acce_target = (CTAS == 2) ? map_to_cta(acce_bar, 0) : acce_bar;
-        uint32_t it = 0;
+        uint32_t it = 0;                                     // accumulation chains seen so far
         bool ok = true;
-        for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++it) {
+        for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
             uint32_t tm, tn;
             tile_coords(t, p, tm, tn);
-            const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
-            if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
-                if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
-                ok = false;
-                break;
-            }
-            tc_fence_after_sync();
             const uint32_t row = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32 + lane;
-            const uint32_t colbase = tn * Cfg::BN;
-            const uint32_t taddr = tmem_base + a * Cfg::BN + ((quarter * 32u) << 16);
+            const uint32_t colbase = tn * Cfg::BN + colpart * Cfg::EPI_COLS;
+            if constexpr (Cfg::PROMOTE) {
+                float sum[Cfg::EPI_COLS];
+#pragma unroll
+                for (int i = 0; i < Cfg::EPI_COLS; ++i) sum[i] = 0.f;
+                for (uint32_t c = 0; c < n_chunks && ok; ++c, ++it) {
+                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                    if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
+                        if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t taddr = tmem_base + a * Cfg::BN + colpart * Cfg::EPI_COLS + ((quarter * 32u) << 16);
+#pragma unroll
+                    for (int q = 0; q < Cfg::EPI_COLS / 32; ++q) {
+                        if (colbase + q * 32 < p.N) {        // uniform across the warp
+                            uint32_t v[32];
+                            tmem_ld_32x32(taddr + q * 32, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) sum[q * 32 + i] += __uint_as_float(v[i]);
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CTAS == 2) mbar_arrive_cluster(acce_target + 8 * a);
+                        else mbar_arrive(acce_bar + 8 * a);
+                    }
+                }
+                if (ok && row < p.M) {
+#pragma unroll
+                    for (int q = 0; q < Cfg::EPI_COLS / 32; ++q) {
+                        const uint32_t col0 = colbase + q * 32;
+                        if (col0 < p.N) {
+                            float part[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) part[i] = sum[q * 32 + i];
+                            store_chunk<KIND>(p, row, col0, part);
+                        }
+                    }
+                }
+            } else {
+                const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
+                    if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + a * Cfg::BN + ((quarter * 32u) << 16);
 #pragma unroll 1
-            for (uint32_t c = 0; c < Cfg::BN / 32; ++c) {
-                const uint32_t col0 = colbase + c * 32;
-                if (col0 >= p.N) break;                      // uniform across the warp
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + c * 32, v);
-                tmem_ld_wait();
-                if (row < p.M) store_chunk<KIND>(p, row, col0, v);
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (CTAS == 2) mbar_arrive_cluster(acce_target + 8 * a);
-                else mbar_arrive(acce_bar + 8 * a);
+                for (uint32_t c = 0; c < Cfg::EPI_COLS / 32; ++c) {
+                    const uint32_t col0 = colbase + c * 32;
+                    if (col0 >= p.N) break;                  // uniform across the warp
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    float acc[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(v[i]);
+                    if (row < p.M) store_chunk<KIND>(p, row, col0, acc);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CTAS == 2) mbar_arrive_cluster(acce_target + 8 * a);
+                    else mbar_arrive(acce_bar + 8 * a);
+                }
+                ++it;
             }
         }
     }

@@ -163,10 +163,13 @@ def test_baseline_cfg5_shape_fp16_properties(G, dev):
     rows = [0, 127, 128, 255, 256, 4095, 8191] + list(np.random.default_rng(2).integers(0, M, 9))
     A_rows, Bh = tA[rows].cpu().numpy(), tB.cpu().numpy()
     _rows_check(D[rows].cpu().numpy(), A_rows, Bh, 1e-2)
-    # alpha = 2 doubles every product exactly, so the fp16 results double exactly (no overflow here)
+    # alpha = 2 doubles the fp32 accumulator exactly, so every fp16 result that is a normal number
+    # doubles exactly (subnormal results round on a fixed grid and are left out; nothing overflows)
     D2 = G.gemm(tA, tB, alpha=2.0)
     torch.cuda.synchronize()
-    assert torch.equal(D2.float(), D.float() * 2)
+    normal = D.float().abs() >= 2.0 ** -13
+    assert normal.float().mean() > 0.99
+    assert torch.equal(D2.float()[normal], (D.float() * 2)[normal])
     # A . I == A bit for bit (one exact product per output, fp32 accumulate, exact fp16 store)
     eye = torch.eye(K, dtype=torch.float16, device=dev)
     assert torch.equal(G.gemm(tA, eye), tA)
@@ -217,7 +220,7 @@ def test_host_pointer_entry_point(G, dev, dt, pinned):
     if pinned:
         tA, tB, tC = (torch.from_numpy(np.pad(x, ((0, 0), (0, 5)))).pin_memory()[:, : x.shape[1]] for x in (A, B, C))
     st = G.new_status(dev)
-    out = torch.full((M, N + 3), float("nan"), dtype=tA.dtype)
+    out = torch.full((M, N + 3), complex("nan+nanj") if tA.is_complex() else float("nan"), dtype=tA.dtype)
     if pinned:
         out = out.pin_memory()
     G.gemm_host(tA, tB, tC, alpha, beta, out=out[:, :N], status=st, device=dev)
@@ -226,6 +229,7 @@ def test_host_pointer_entry_point(G, dev, dt, pinned):
     assert torch.isnan(o[:, N:]).all()
     _check(out[:, :N].numpy(), A, B, C, alpha, beta)
     # same numbers as the device-pointer entry point, bit for bit
-    D = G.gemm(tA.to(dev), tB.to(dev), tC.to(dev), alpha, beta)
+    gA, gB, gC = (Guarded(torch, x, dev) for x in (A, B, C))
+    D = G.gemm(gA.view, gB.view, gC.view, alpha, beta)
     torch.cuda.synchronize()
     assert torch.equal(D.cpu(), out[:, :N])

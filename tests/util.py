@@ -41,7 +41,8 @@ class Guarded:
         t = torch.from_numpy(np.ascontiguousarray(host))
         p = pitch_elems(c, t.element_size())
         self.red = red_rows
-        self.buf = torch.full((r + 2 * red_rows, p), float("nan"), dtype=t.dtype, device=device)
+        nan = complex("nan+nanj") if t.is_complex() else float("nan")
+        self.buf = torch.full((r + 2 * red_rows, p), nan, dtype=t.dtype, device=device)
         self.view = self.buf[red_rows:red_rows + r, :c]
         if fill_logical is None:
             self.view.copy_(t.to(device))
