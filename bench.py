@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (`cfg5`): fp16 GEMM, fp32 accumulate, fp16 output, M=65536 N=16384 K=16384,
+A ~ N(0, 0.02) row-sharded over the N GPUs, B on the owner (rank 0), D gathered on the owner.  This
+is the configuration whose TFLOPS are quoted at 1/2/4/8 GPUs; total work is fixed (strong scaling).
+One step = B broadcast in panels + every rank's GEMM + gather of D on the owner (at N=1: one GEMM).
+Inputs are synthetic, generated on the device; they (4.5 GiB) are far larger than the 126 MB L2, so
+no L2 flush is needed between steps.
+
+Prints ONE JSON line on rank 0.  Under torchrun (N > 1) ranks talk NCCL; timing is CUDA events on
+the launching stream, bracketed by barrier + synchronize, max over ranks.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (dtype, M, N, K, distribution, sigma, fused, flop factor)
+    "cfg5": ("float16", 65536, 16384, 16384, "normal", 0.02, False, 2),
+    "fp16_16384": ("float16", 16384, 16384, 16384, "normal", 0.02, False, 2),
+    "cfg2": ("float32", 8192, 8192, 8192, "uniform", 1.0, False, 2),
+    "cfg3": ("float32", 4099, 3001, 2053, "normal", 1.0, True, 2),
+    "cfg4": ("complex64", 4096, 4096, 4096, "uniform", 1.0, False, 8),
+    "cfg1": ("float32", 1024, 1024, 1024, "uniform", 1.0, False, 2),
+}
+DESCR = {
+    "cfg5": "fp16 GEMM (fp32 accumulate, fp16 out) M=65536 N=16384 K=16384, A row-sharded, B broadcast, D gathered on owner",
+    "fp16_16384": "fp16 GEMM (fp32 accumulate, fp16 out) M=N=K=16384",
+    "cfg2": "fp32 GEMM (3xTF32) M=N=K=8192, U[-1,1]",
+    "cfg3": "fp32 fused D=A.B+C (3xTF32) M=4099 N=3001 K=2053, N(0,1), alpha=beta=1",
+    "cfg4": "complex fp32 GEMM (3xTF32, 4 real products) M=N=K=4096, U[-1,1]",
+    "cfg1": "fp32 GEMM (3xTF32) M=N=K=1024, U[-1,1]",
+}
+ARITH = {"float16": "f16 (fp32 accumulate)", "float32": "3xTF32 (fp32 accumulate)", "complex64": "3xTF32 (fp32 accumulate)"}
+
+
+def peaks():
+    """Measured denominators for this pool; fallback = an earlier measurement (1.59 PFLOP/s bf16)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"bf16": float(d["bf16_tflops"]), "bf16_sustained": float(d.get("bf16_tflops_sustained", 0)) or None,
+                "source": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def tensor_peak(dtype, pk):
+    """fp16 runs at the bf16 rate; TF32 at half of it; 3xTF32 executes three MMAs per useful one."""
+    return pk["bf16"] if dtype == "float16" else pk["bf16"] / 2 / 3
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()          # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], None, set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            if not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def gen(torch, shape, dtype, dist_name, sigma, device, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    def real():
+        if dist_name == "uniform":
+            return torch.rand(shape, device=device, generator=g) * 2 - 1
+        return torch.randn(shape, device=device, generator=g) * sigma
+    if dtype == "complex64":
+        return torch.complex(real(), real())
+    x = real()
+    return x.half() if dtype == "float16" else x
+
+
+def cpu_baseline(workload, bounded_rows=1024):
+    """The reference's own CPU GEMM (oracle/_ref) on a bounded sample of the workload, timed on this
+    host's cores; the C restatement when that build is absent.  Reported beside the GPU number."""
+    from oracle import binding as ob
+    dtype, M, N, K, _, sigma, _, ff = WORKLOADS[workload]
+    rows = min(M, bounded_rows)
+    # keep the sample near 10-30 s of CPU work: shrink N for the big shapes' sample too
+    cols = N
+    flops = ff * rows * cols * K
+    if ob.ref_available():
+        code = 5 if dtype == "complex64" else 1
+        note = ""
+        if dtype == "float16":
+            note = " (the reference has no fp16 CPU GEMM: fp16 values widened to fp32, its fp32 path)"
+        r = ob.ref_cpu_gemm_time(code, rows, cols, K, threads=16, repeats=2, sigma=sigma)
+        best = min(r["times"])
+        return {"value": flops / best / 1e12, "unit": "TFLOPS", "cores": r["threads"], "kind": "reference",
+                "sample": f"de::blas::cpu::GEMM on rows 0..{rows - 1} of A ({rows}x{cols}x{K}){note}, best of 2 calls",
+                "seconds": best, "host_cpus": os.cpu_count()}
+    rows = min(rows, 256)
+    r = ob.port_gemm_time(rows, cols, K, sigma=sigma)
+    best = min(r["times"])
+    return {"value": ff * rows * cols * K / best / 1e12, "unit": "TFLOPS", "cores": r["threads"], "kind": "port",
+            "sample": f"oracle/gemm_oracle.c (fp32-accumulate restatement) on rows 0..{rows - 1} ({rows}x{cols}x{K})",
+            "seconds": best, "host_cpus": os.cpu_count()}
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU implementation of the path on this host's cores."""
+    if rank != 0:
+        return
+    dtype, M, N, K, _, sigma, fused, ff = WORKLOADS[args.workload]
+    from oracle import binding as ob
+    times, info = [], None
+    for i in range(args.warmup + args.steps):
+        info = cpu_baseline(args.workload, bounded_rows=512)
+        if i >= args.warmup:
+            times.append(info["seconds"])
+    rows = min(M, 512)
+    flops = ff * rows * N * K
+    t = sum(times) / len(times)
+    val = flops / t / 1e12
+    line = {
+        "impl": "reference", "metric": "GEMM TFLOPS", "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 (AVX2 FMA)", "data": "synthetic",
+        "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
+                   "step": info["sample"]},
+        "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": info["cores"], "kind": info["kind"],
+                         "sample": info["sample"], "host_cpus": info["host_cpus"]},
+        "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
+    """Kernel-level timing of one single-GPU configuration (device-resident operands)."""
+    dtype, M, N, K, dist_name, sigma, fused, ff = WORKLOADS[workload]
+    A = gen(torch, (M, K), dtype, dist_name, sigma, device, 100)
+    B = gen(torch, (K, N), dtype, dist_name, sigma, device, 101)
+    C = gen(torch, (M, N), dtype, dist_name, sigma, device, 102) if fused else None
+    out = torch.empty((M, N), dtype=A.dtype, device=device)
+    need = capi.workspace_bytes(G._DTYPES[A.dtype], M, N, K)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+    st = G.new_status(device)
+    run = lambda: G.gemm(A, B, C, 1.0 if fused else None, 1.0 if fused else None, out=out, workspace=ws, status=st)
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize(device)
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ts.append(e0.elapsed_time(e1))
+    assert int(st.item()) == 0, "kernel reported a time-out"
+    flops = ff * M * N * K
+    med = statistics.median(ts)
+    return {"workload": workload, "description": DESCR[workload], "ms_median": med, "ms_best": min(ts),
+            "tflops": flops / med / 1e9, "tflops_best": flops / min(ts) / 1e9,
+            "launches_per_call": capi.lib.decxb200_last_launch_count(), "arithmetic": ARITH[dtype]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
+    ap.add_argument("--panels", type=int, default=4, help="column panels of B in the sharded path")
+    ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from decx_b200 import capi, gemm as G           # raises if the CUDA library is missing: no fallback
+    from decx_b200.sharded import ShardedGemm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the GEMM path has no CPU fallback")
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    dtype, M, N, K, dist_name, sigma, fused, ff = WORKLOADS[args.workload]
+    if world > 1 and fused:
+        raise SystemExit("the sharded path covers plain A.B; run fused workloads with --gpus 1")
+    tdtype = {"float16": torch.float16, "float32": torch.float32, "complex64": torch.complex64}[dtype]
+    flops = float(ff) * M * N * K
+    pk = peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ------------------------------------------------------------ device-resident measurement
+    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=args.panels, gather=args.gather, device=device)
+    if sg.nrows:
+        sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
+    if sg.is_owner:
+        sg.B.copy_(gen(torch, (K, N), dtype, dist_name, sigma, device, 5))
+    if world == 1 and fused:
+        pass
+    for _ in range(args.warmup):
+        sg.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t0 = time.perf_counter()
+    launches = 0
+    for i in range(args.steps):
+        ev[i][0].record()
+        sg.step()
+        ev[i][1].record()
+        launches += sg.launches
+    barrier()
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    dev_ms = ev[0][0].elapsed_time(ev[-1][1])
+    total_ms = max_over_ranks(dev_ms)
+    step_ms = total_ms / args.steps
+    value = flops * args.steps / (total_ms * 1e-3) / 1e12
+    assert int(sg.status.item()) == 0, f"kernel status {int(sg.status.item()):#x}"
+    total_launches = int(max_over_ranks(float(launches)) * world) if world > 1 else launches
+
+    # dominant kernel alone (no communication): CUDA events around this rank's GEMM launches
+    kern_ms = []
+    if sg.nrows:
+        for _ in range(2):
+            for j in range(len(sg.panels)):
+                sg._panel_gemm(j)
+        torch.cuda.synchronize(device)
+        for _ in range(3):
+            for j in range(len(sg.panels)):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                sg._panel_gemm(j)
+                e1.record()
+                torch.cuda.synchronize(device)
+                kern_ms.append(e0.elapsed_time(e1))
+    barrier()
+    flops_per_launch = flops / world / len(sg.panels)
+    kern_avg = max_over_ranks(sum(kern_ms) / len(kern_ms) if kern_ms else 0.0)
+    achieved = flops_per_launch / (kern_avg * 1e-3) / 1e12 if kern_avg else 0.0
+    peak = tensor_peak(dtype, pk)
+
+    # ------------------------------------------------------------ end to end, host buffers
+    if world == 1:
+        esz = torch.empty(0, dtype=tdtype).element_size()
+        hA = torch.empty((M, K), dtype=tdtype).pin_memory()
+        hB = torch.empty((K, N), dtype=tdtype).pin_memory()
+        hD = torch.empty((M, N), dtype=tdtype).pin_memory()
+        hA.copy_(sg.A)
+        hB.copy_(sg.B)
+        arena = torch.empty(G.host_arena_bytes(tdtype, M, N, K), dtype=torch.uint8, device=device)
+        st = G.new_status(device)
+        for _ in range(2):
+            G.gemm_host(hA, hB, out=hD, arena=arena, status=st, device=device)
+        torch.cuda.synchronize(device)
+        e2e_steps = args.steps
+        t0e = time.perf_counter()
+        for _ in range(e2e_steps):
+            G.gemm_host(hA, hB, out=hD, arena=arena, status=st, device=device)
+        torch.cuda.synchronize(device)
+        e2e_s = (time.perf_counter() - t0e) / e2e_steps
+        h2d, d2h = (M * K + K * N) * esz, M * N * esz
+        e2e_launches = capi.lib.decxb200_last_launch_count() * e2e_steps
+        del hA, hB, hD, arena
+    else:
+        esz = torch.empty(0, dtype=tdtype).element_size()
+        hA = torch.empty((max(sg.nrows, 1), K), dtype=tdtype).pin_memory()[: sg.nrows]
+        hA.copy_(sg.A)
+        hB = hD = None
+        if sg.is_owner:
+            hB = torch.empty((K, N), dtype=tdtype).pin_memory()
+            hB.copy_(sg.B)
+            hD = torch.empty((M, N), dtype=tdtype).pin_memory()
+
+        def e2e_step():
+            if sg.is_owner:
+                sg.B.copy_(hB, non_blocking=True)
+            if sg.nrows:
+                sg.A.copy_(hA, non_blocking=True)
+            sg.step()
+            if sg.is_owner:
+                hD.copy_(sg.D, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e2e_steps = args.steps
+        t0e = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = max_over_ranks((time.perf_counter() - t0e) / e2e_steps)
+        h2d, d2h = (M * K + K * N) * esz, M * N * esz
+        e2e_launches = sg.launches * e2e_steps * world
+    e2e_val = flops / e2e_s / 1e12
+
+    line = {
+        "metric": "GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": ARITH[dtype], "data": "synthetic (seeded, generated on the device)",
+        "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
+                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels, gather={sg.gather}" if world > 1 else ""),
+                   "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30)},
+        "pct_of_peak": {"value": 100 * value / (world * peak), "denominator_tflops": world * peak,
+                        "which": f"{pk['source']} bf16 burst x {world} GPU(s)" + ("" if dtype == "float16" else ", /2 for TF32, /3 for 3xTF32"),
+                        "of_sustained": (100 * value / (world * pk["bf16_sustained"] / (1 if dtype == "float16" else 6))) if pk["bf16_sustained"] else None},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, world)),
+                     "kernel": "gemm_tcgen05_kernel<%d,2>" % (0 if dtype == "float16" else 1),
+                     "launch_ms": kern_avg, "flops_per_launch": flops_per_launch,
+                     "peak_source": f"{pk['source']}: bf16 burst {pk['bf16']} TFLOP/s" + ("" if dtype == "float16" else " /6 (TF32 rate, three MMAs per product)")},
+        "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s * 1e3, "how": "decxb200_gemm_host (pinned host A, B, D; copies pipelined with the GEMM)" if world == 1
+                else "pinned host A shards / B / D, copies + sharded step + D to host on the owner"},
+        "gpu_launches": total_launches,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_extras:
+        others = []
+        for w in ("fp16_16384", "cfg2", "cfg4", "cfg3", "cfg1"):
+            if w != args.workload:
+                r = time_single(torch, G, capi, w, device)
+                wp = tensor_peak(WORKLOADS[w][0], pk)
+                r["pct_of_peak"] = 100 * r["tflops"] / wp
+                r["peak_tflops"] = wp
+                others.append(r)
+        line["other_configs"] = others
+    sg.close()
+    if rank == 0 and not args.no_extras and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args.workload)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu
+# captures summarised under profiles/ (None = not captured for that configuration)
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+if __name__ == "__main__":
+    main()

@@ -37,6 +37,17 @@ def _load():
     lib.decxb200_gemm_host_arena_bytes.argtypes = [ci, u32, u32, u32, ci]
     lib.decxb200_gemm_host.restype = ci
     lib.decxb200_gemm_host.argtypes = [ci, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
+    pvp = ctypes.POINTER(ctypes.c_void_p)
+    lib.decxb200_ipc_alloc.restype = ci
+    lib.decxb200_ipc_alloc.argtypes = [sz, pvp]
+    lib.decxb200_ipc_free.restype = ci
+    lib.decxb200_ipc_free.argtypes = [vp]
+    lib.decxb200_ipc_export.restype = ci
+    lib.decxb200_ipc_export.argtypes = [vp, ctypes.c_char_p]
+    lib.decxb200_ipc_open.restype = ci
+    lib.decxb200_ipc_open.argtypes = [ctypes.c_char_p, pvp]
+    lib.decxb200_ipc_close.restype = ci
+    lib.decxb200_ipc_close.argtypes = [vp]
     lib.decxb200_last_launch_count.restype = ci
     lib.decxb200_last_launch_count.argtypes = []
     lib.decxb200_strerror.restype = ctypes.c_char_p
@@ -51,6 +62,7 @@ lib = _load()
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
+    "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
 ]
 

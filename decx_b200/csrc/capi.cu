@@ -484,6 +484,40 @@ int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K, c
                             workspace_bytes, status, 0, 0);
 }
 
+int decxb200_ipc_alloc(size_t bytes, void** dptr) {
+    if (dptr == nullptr || bytes == 0) return DECXB200_EINVAL;
+    const cudaError_t e = cudaMalloc(dptr, bytes);   // a whole allocation: IPC handles name allocations
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+int decxb200_ipc_free(void* dptr) {
+    const cudaError_t e = cudaFree(dptr);
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+int decxb200_ipc_export(void* dptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (dptr == nullptr || handle == nullptr) return DECXB200_EINVAL;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, dptr);
+    if (e != cudaSuccess) return int(e);
+    memcpy(handle, &h, 64);
+    return 0;
+}
+
+int decxb200_ipc_open(const unsigned char handle[64], void** peer_ptr) {
+    if (handle == nullptr || peer_ptr == nullptr) return DECXB200_EINVAL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    const cudaError_t e = cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+int decxb200_ipc_close(void* peer_ptr) {
+    const cudaError_t e = cudaIpcCloseMemHandle(peer_ptr);
+    return e == cudaSuccess ? 0 : int(e);
+}
+
 int decxb200_last_launch_count(void) { return t_launches; }
 
 const char* decxb200_strerror(int code) {

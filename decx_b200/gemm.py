@@ -107,3 +107,13 @@ def gemm_host(A, B, C=None, alpha=None, beta=None, out=None, arena=None, status=
             status.data_ptr() if status is not None else None)
     capi.check(code)
     return out
+
+
+def gemm_raw(dt, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd, alpha=None, beta=None,
+             ws_ptr=None, ws_bytes=0, status_ptr=None, stream=0, cta_group=0, max_ctas=0):
+    """The C ABI with raw device addresses (used where D lives in another GPU's memory)."""
+    _a, pa = _scalar(dt, alpha)
+    _b, pb = _scalar(dt, beta if c_ptr else None)
+    capi.check(capi.lib.decxb200_gemm_ex(dt, stream, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd,
+                                         pa, pb, ws_ptr, ws_bytes, status_ptr, cta_group, max_ctas))
+    return capi.lib.decxb200_last_launch_count()

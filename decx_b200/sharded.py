@@ -1,0 +1,221 @@
+"""Row-sharded GEMM over the GPUs of one box, one process per GPU (torch.distributed).
+
+    D (M x N, on the owner)  =  A (M x K, rows partitioned over the ranks)  .  B (K x N, on the owner)
+
+The reference is single-GPU (its sources hold no cudaSetDevice, peer copy or collective), so this
+layer is new surface on top of the same per-GPU GEMM.  One step is:
+
+  1. B travels from the owner to every rank in column panels: the owner packs panel j into a
+     contiguous K x Np buffer and NCCL broadcasts it (NVLink / NVSwitch) on a communication stream;
+  2. as soon as panel j has landed in this rank's own HBM, the rank's GEMM for that panel runs on the
+     compute stream, D[rows of this rank, panel j] = A_r . B[:, panel j]  (its TMA loads read local
+     memory only, none of them uses cluster multicast), while panel j+1 is still in flight;
+  3. gather on the owner, mode "peer" (default on GPUs): the owner's D is exported through a CUDA IPC
+     handle and each rank's GEMM epilogue stores its rows straight into it over NVLink, so the
+     gather is fused into the kernel and finished when the kernels are; mode "collective": each rank
+     keeps a local D shard and sends it to the owner afterwards (plain point-to-point; this is the
+     form the CPU tests run over gloo with an injected host GEMM);
+  4. a barrier across the ranks closes the step.
+
+Rows are dealt in multiples of 256 (the CTA-pair tile height), so every rank runs whole tiles.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+ROW_ALIGN = 256
+COL_ALIGN = 256
+
+
+def row_ranges(M, world, align=ROW_ALIGN):
+    """[(first_row, rows)] per rank: equal blocks of whole `align`-row tiles, the remainder on the
+    last ranks that still get rows; ranks beyond the data get (M, 0)."""
+    blocks = (M + align - 1) // align
+    per = (blocks + world - 1) // world
+    out = []
+    for r in range(world):
+        start = min(M, r * per * align)
+        stop = min(M, (r + 1) * per * align)
+        out.append((start, stop - start))
+    return out
+
+
+def panel_plan(N, panels, align=COL_ALIGN):
+    """[(first_col, cols)] of the column panels of B: `panels` near-equal multiples of `align`."""
+    blocks = (N + align - 1) // align
+    panels = max(1, min(panels, blocks))
+    base, extra = divmod(blocks, panels)
+    out, c = [], 0
+    for j in range(panels):
+        w = (base + (1 if j < extra else 0)) * align
+        w = min(w, N - c)
+        out.append((c, w))
+        c += w
+    assert c == N
+    return out
+
+
+class _RawCuda:
+    """Lets torch view memory that was allocated through the C ABI (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+_TYPESTR = {torch.float16: "<f2", torch.float32: "<f4", torch.complex64: "<c8"}
+
+
+class ShardedGemm:
+    """Buffers and schedule of one sharded problem; ``step()`` runs it once.
+
+    After construction fill ``self.A`` (this rank's rows of A) and, on the owner, ``self.B``.
+    The owner reads the result from ``self.D`` (M x N).  ``gemm_fn(A, Bp, out)`` replaces the CUDA
+    GEMM in CPU tests only; on a GPU the C ABI is called and there is no other path.
+    """
+
+    def __init__(self, M, N, K, dtype, group=None, owner=0, panels=4, gather=None, device=None, gemm_fn=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.owner, self.M, self.N, self.K, self.dtype = owner, M, N, K, dtype
+        self.device = torch.device(device if device is not None else "cpu")
+        self.on_gpu = self.device.type == "cuda"
+        if not self.on_gpu and gemm_fn is None:
+            raise RuntimeError("ShardedGemm computes on CUDA devices only (a host GEMM can only be injected by tests)")
+        self.gemm_fn = gemm_fn
+        self.gather = gather or ("peer" if self.on_gpu and self.world > 1 else "collective")
+        self.rows = row_ranges(M, self.world)
+        self.row0, self.nrows = self.rows[self.rank]
+        self.panels = panel_plan(N, panels if self.world > 1 else 1)
+        self.is_owner = self.rank == owner
+        dev = self.device
+        self.A = torch.empty((max(self.nrows, 1), K), dtype=dtype, device=dev)[: self.nrows]
+        self.B = torch.empty((K, N), dtype=dtype, device=dev) if self.is_owner else None
+        if self.world > 1:
+            self.Bp = [torch.empty((K, w), dtype=dtype, device=dev) for _, w in self.panels]
+        else:
+            self.Bp = [self.B]
+        self.launches = 0
+        self._peer_base = None
+        self._owned = None
+        esz = torch.empty(0, dtype=dtype).element_size()
+        self._esz = esz
+        if self.on_gpu:
+            from . import capi, gemm as G
+            self._capi, self._G = capi, G
+            self._dt = G._DTYPES[dtype]
+            self.status = G.new_status(dev)
+            need = max((capi.workspace_bytes(self._dt, max(self.nrows, 1), w, K) for _, w in self.panels), default=0)
+            self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+            self._ws_bytes = need
+            self.comm_stream = torch.cuda.Stream(device=dev)
+            self.events = [torch.cuda.Event() for _ in self.panels]
+        if self.gather == "peer":
+            self._setup_peer_d()
+        else:
+            self.D = torch.empty((M, N), dtype=dtype, device=dev) if self.is_owner else None
+            self.D_local = self.D[self.row0:self.row0 + self.nrows] if self.is_owner else \
+                torch.empty((max(self.nrows, 1), N), dtype=dtype, device=dev)[: self.nrows]
+
+    # ------------------------------------------------------------------ peer-visible D on the owner
+    def _setup_peer_d(self):
+        capi = self._capi
+        handle = torch.zeros(64, dtype=torch.uint8)
+        with torch.cuda.device(self.device):
+            if self.is_owner:
+                p = ctypes.c_void_p()
+                capi.check(capi.lib.decxb200_ipc_alloc(self.M * self.N * self._esz, ctypes.byref(p)))
+                self._owned = p.value
+                buf = ctypes.create_string_buffer(64)
+                capi.check(capi.lib.decxb200_ipc_export(p.value, buf))
+                handle = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+            h = handle.to(self.device)
+            dist.broadcast(h, src=self.owner, group=self.group)
+            if self.is_owner:
+                base = self._owned
+                self.D = torch.as_tensor(_RawCuda(base, (self.M, self.N), _TYPESTR[self.dtype]), device=self.device)
+            else:
+                p = ctypes.c_void_p()
+                capi.check(capi.lib.decxb200_ipc_open(bytes(h.cpu().numpy().tobytes()), ctypes.byref(p)))
+                self._peer_base = base = p.value
+                self.D = None
+            self._d_ptr = base + self.row0 * self.N * self._esz
+
+    def close(self):
+        if self.on_gpu:
+            torch.cuda.synchronize(self.device)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+        if self._peer_base is not None:
+            self._capi.lib.decxb200_ipc_close(self._peer_base)
+            self._peer_base = None
+        if self._owned is not None:
+            self.D = None
+            self._capi.lib.decxb200_ipc_free(self._owned)
+            self._owned = None
+
+    # ------------------------------------------------------------------ one step
+    def _panel_gemm(self, j):
+        c0, w = self.panels[j]
+        if self.nrows == 0:
+            return
+        if self.gemm_fn is not None:
+            self.gemm_fn(self.A, self.Bp[j], self.D_local[:, c0:c0 + w])
+            return
+        G = self._G
+        if self.gather == "peer":
+            d_ptr = self._d_ptr + c0 * self._esz
+        else:
+            d_ptr = self.D_local.data_ptr() + c0 * self._esz
+        ldb = self.Bp[j].stride(0)
+        self.launches += G.gemm_raw(self._dt, self.nrows, w, self.K, self.A.data_ptr(), self.A.stride(0),
+                                    self.Bp[j].data_ptr() + (c0 * self._esz if self.world == 1 else 0), ldb,
+                                    None, 0, d_ptr, self.N,
+                                    ws_ptr=self.workspace.data_ptr() if self._ws_bytes else None,
+                                    ws_bytes=self._ws_bytes, status_ptr=self.status.data_ptr(),
+                                    stream=torch.cuda.current_stream(self.device).cuda_stream)
+
+    def step(self):
+        """Broadcast B, multiply, gather on the owner.  Asynchronous on a GPU: the caller synchronises."""
+        self.launches = 0
+        if self.world == 1:
+            self.Bp = [self.B]
+            self._panel_gemm(0)
+            return
+        if self.on_gpu:
+            with torch.cuda.device(self.device):
+                cur = torch.cuda.current_stream(self.device)
+                self.comm_stream.wait_stream(cur)
+                with torch.cuda.stream(self.comm_stream):
+                    for j, (c0, w) in enumerate(self.panels):
+                        if self.is_owner:
+                            self.Bp[j].copy_(self.B[:, c0:c0 + w])
+                        dist.broadcast(self.Bp[j], src=self.owner, group=self.group)
+                        self.events[j].record(self.comm_stream)
+                for j in range(len(self.panels)):
+                    cur.wait_event(self.events[j])
+                    self._panel_gemm(j)
+                if self.gather == "collective":
+                    self._collect()
+                dist.barrier(group=self.group)      # every rank's rows have reached the owner
+        else:
+            for j, (c0, w) in enumerate(self.panels):
+                if self.is_owner:
+                    self.Bp[j].copy_(self.B[:, c0:c0 + w])
+                dist.broadcast(self.Bp[j], src=self.owner, group=self.group)
+                self._panel_gemm(j)
+            self._collect()
+            dist.barrier(group=self.group)
+
+    def _collect(self):
+        """Mode "collective": full-width row blocks are contiguous in the owner's D, one message per rank."""
+        if self.is_owner:
+            reqs = []
+            for r, (r0, n) in enumerate(self.rows):
+                if r != self.owner and n > 0:
+                    reqs.append(dist.irecv(self.D[r0:r0 + n], src=r, group=self.group))
+            for q in reqs:
+                q.wait()
+        elif self.nrows > 0:
+            dist.send(self.D_local, dst=self.owner, group=self.group)

@@ -110,6 +110,21 @@ DECXB200_API int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t 
                                     const void* alpha, const void* beta,
                                     void* arena, size_t arena_bytes, unsigned* status);
 
+/*
+ * Peer-visible device buffers for the row-sharded multi-GPU GEMM (one process per GPU).
+ * The owner of the result allocates D with decxb200_ipc_alloc and exports a 64-byte handle;
+ * every other rank opens it and passes `peer_ptr + its row offset` as the D argument of
+ * decxb200_gemm, so the GEMM epilogue stores its rows straight into the owner's memory over
+ * NVLink ("C gathered on the owner" with no separate gather step).  The reference is
+ * single-GPU (no cudaSetDevice / peer / collective call anywhere in its sources), so these
+ * have no counterpart there.
+ */
+DECXB200_API int decxb200_ipc_alloc(size_t bytes, void** dptr);
+DECXB200_API int decxb200_ipc_free(void* dptr);
+DECXB200_API int decxb200_ipc_export(void* dptr, unsigned char handle[64]);
+DECXB200_API int decxb200_ipc_open(const unsigned char handle[64], void** peer_ptr);
+DECXB200_API int decxb200_ipc_close(void* peer_ptr);
+
 /* Number of kernels the last decxb200_gemm* call of this thread launched (pre-passes included). */
 DECXB200_API int decxb200_last_launch_count(void);
 

@@ -155,3 +155,57 @@ def ref_cpu_gemm(A, B, threads=8, repeats=1, tmpdir=None):
         if int(z["rc"][0]) != 0:
             raise RuntimeError("reference harness rejected the call")
         return z["D"], z["times"], int(z["threads"][0])
+
+
+_REF_TIME_CHILD = r"""
+import ctypes, json, sys, time
+import numpy as np
+so, dtype, M, N, K, threads, repeats, seed, sigma = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]), int(sys.argv[6]), int(sys.argv[7]), int(sys.argv[8]), float(sys.argv[9])
+L = ctypes.CDLL(so)
+L.decx_ref_max_threads.restype = ctypes.c_uint
+rng = np.random.default_rng(seed)
+def mk(r, c):
+    x = rng.standard_normal((r, c), dtype=np.float32) * np.float32(sigma)
+    if dtype == 5:
+        x = (x + 1j * rng.standard_normal((r, c), dtype=np.float32) * np.float32(sigma)).astype(np.complex64)
+    return x
+A, B = mk(M, K), mk(K, N)
+D = np.zeros((M, N), dtype=A.dtype)
+times = np.zeros(repeats, dtype=np.float64)
+threads = min(threads, int(L.decx_ref_max_threads()))
+vp = ctypes.c_void_p
+L.decx_ref_cpu_gemm.argtypes = [ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, vp, ctypes.c_size_t, vp,
+                                ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_uint, ctypes.c_int, vp]
+rc = L.decx_ref_cpu_gemm(dtype, M, N, K, A.ctypes.data, K, B.ctypes.data, N, D.ctypes.data, N, threads, repeats,
+                         times.ctypes.data)
+print("REFTIME " + json.dumps({"rc": rc, "threads": threads, "times": times.tolist(), "finite": bool(np.isfinite(D).all())}))
+"""
+
+
+def ref_cpu_gemm_time(dtype_code, M, N, K, threads=16, repeats=2, seed=0, sigma=1.0):
+    """Time the reference's de::blas::cpu::GEMM on synthetic data generated inside a child process
+    (one shape per process).  Returns {"threads", "times" (seconds per call)}."""
+    if not ref_available():
+        raise RuntimeError("oracle/_ref/libdecx_ref_cpu.so has not been built")
+    r = subprocess.run([sys.executable, "-c", _REF_TIME_CHILD, REF_SO, str(dtype_code), str(M), str(N), str(K),
+                        str(threads), str(repeats), str(seed), str(sigma)], check=True, capture_output=True, text=True)
+    line = [l for l in r.stdout.splitlines() if l.startswith("REFTIME ")][-1]
+    res = json.loads(line[len("REFTIME "):])
+    if res["rc"] != 0 or not res["finite"]:
+        raise RuntimeError(f"reference harness failed: {res}")
+    return res
+
+
+def port_gemm_time(M, N, K, repeats=1, seed=0, sigma=1.0):
+    """Time the C restatement (fp16 inputs, fp32 accumulate) -- the fallback CPU baseline where the
+    reference build is absent."""
+    import time
+    rng = np.random.default_rng(seed)
+    A = (rng.standard_normal((M, K), dtype=np.float32) * sigma).astype(np.float16)
+    B = (rng.standard_normal((K, N), dtype=np.float32) * sigma).astype(np.float16)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        gemm(A, B)
+        times.append(time.perf_counter() - t0)
+    return {"threads": os.cpu_count() or 1, "times": times}
