@@ -221,8 +221,12 @@ def main():
     ap.add_argument("--panels", type=int, default=4, help="column panels of B in the sharded path")
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-resident loop only (no end-to-end leg, no extras): the command profiled under ncu")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.kernel_only else args.warmup
+    if args.kernel_only:
+        args.no_extras = True
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -251,6 +255,7 @@ def main():
     tdtype = {"float16": torch.float16, "float32": torch.float32, "complex64": torch.complex64}[dtype]
     flops = float(ff) * M * N * K
     pk = peaks()
+    esz = torch.empty(0, dtype=tdtype).element_size()
 
     def barrier():
         if world > 1:
@@ -320,7 +325,10 @@ def main():
     peak = tensor_peak(dtype, pk)
 
     # ------------------------------------------------------------ end to end, host buffers
-    if world == 1:
+    if args.kernel_only:
+        e2e_val = e2e_s = None
+        h2d = d2h = 0
+    elif world == 1:
         esz = torch.empty(0, dtype=tdtype).element_size()
         hA = torch.empty((M, K), dtype=tdtype).pin_memory()
         hB = torch.empty((K, N), dtype=tdtype).pin_memory()
@@ -370,7 +378,8 @@ def main():
         e2e_s = max_over_ranks((time.perf_counter() - t0e) / e2e_steps)
         h2d, d2h = (M * K + K * N) * esz, M * N * esz
         e2e_launches = sg.launches * e2e_steps * world
-    e2e_val = flops / e2e_s / 1e12
+    if e2e_s is not None:
+        e2e_val = flops / e2e_s / 1e12
 
     line = {
         "metric": "GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
@@ -388,7 +397,7 @@ def main():
                      "launch_ms": kern_avg, "flops_per_launch": flops_per_launch,
                      "peak_source": f"{pk['source']}: bf16 burst {pk['bf16']} TFLOP/s" + ("" if dtype == "float16" else " /6 (TF32 rate, three MMAs per product)")},
         "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s * 1e3, "how": "decxb200_gemm_host (pinned host A, B, D; copies pipelined with the GEMM)" if world == 1
+                "ms_per_step": e2e_s * 1e3 if e2e_s else None, "how": "decxb200_gemm_host (pinned host A, B, D; copies pipelined with the GEMM)" if world == 1
                 else "pinned host A shards / B / D, copies + sharded step + D to host on the owner"},
         "gpu_launches": total_launches,
         "clocks": clocks,

@@ -33,6 +33,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
+    unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
     bool attr_set[2][2] = {{false, false}, {false, false}};
     int max_pairs[2] = {0, 0};
@@ -59,6 +60,27 @@ int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
+}
+
+// B (K x N row-major) as a 3-D tensor (column-in-chunk, k, chunk): chunk c holds columns
+// [c*chunk_cols, (c+1)*chunk_cols), i.e. dimension 2 has a stride of 128 bytes.  A box of
+// (chunk_cols, box_k, box_chunks) then lands in shared memory exactly as box_chunks consecutive
+// 2-D boxes would.  A last, partly filled chunk is read at full width, so the caller must make sure
+// that ld >= round_up(cols, chunk_cols) (or cols % chunk_cols == 0); what it reads beyond `cols`
+// only reaches output columns that are never stored.  Chunks past the last one are zero-filled.
+int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                       uint32_t chunk_cols, uint32_t box_k, uint32_t box_chunks, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return DECXB200_EDRIVER;
+    const uint64_t esz = f16 ? 2 : 4;
+    cuuint64_t dims[3] = {chunk_cols, rows, (cols + chunk_cols - 1) / chunk_cols};
+    cuuint64_t strides[2] = {ld * esz, chunk_cols * esz};
+    cuuint32_t box[3] = {chunk_cols, box_k, box_chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
@@ -90,8 +112,22 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     if (tiles < workers) workers = uint32_t(tiles);
     // group height: balance the A rows and B columns the concurrently running tiles touch
     uint32_t g = (CTAS == 1) ? 16 : 8;
+    if (const char* e = getenv("DECXB200_GROUP_M")) {       // tuning override
+        const int v = atoi(e);
+        if (v > 0) g = uint32_t(v);
+    }
     if (g > p.tiles_m) g = p.tiles_m;
     p.group_m = g;
+
+    // soft lockstep of the persistent CTAs (on unless DECXB200_TILE_SYNC=0); values > 1 set the wait limit in ns
+    static const int sync_env = [] { const char* e = getenv("DECXB200_TILE_SYNC"); return e ? atoi(e) : 1; }();
+    p.sync_on = (sync_env > 0 && tiles > workers) ? 1u : 0u;
+    p.sync_limit_ns = sync_env > 1 ? unsigned(sync_env) : 20000u;
+    if (p.sync_on) {
+        std::lock_guard<std::mutex> lk(g_dev_mutex);
+        p.sync_base = di.ticket_base;
+        di.ticket_base += unsigned(tiles);       // every launch adds exactly one ticket per tile
+    }
 
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -228,7 +264,18 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
     CUtensorMap a0, b0;
     int rc;
     if ((rc = make_map(&a0, true, A, M, K, lda, C1::BK, C1::BM)) != 0) return rc;
-    if ((rc = make_map(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK)) != 0) return rc;
+    // one 3-D load per stage when reading the last column chunk at full width stays inside B's rows
+    p.b_chunked_map = ((N % C1::CHUNK_N) == 0 || ldb >= round_up(N, C1::CHUNK_N)) ? 1 : 0;
+    if (!p.b_chunked_map) {
+        rc = make_map(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK);
+    } else if (cta_group == 1) {
+        rc = make_map_b_chunked(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK, GemmCfg<0, 1>::B_CHUNKS,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+        rc = make_map_b_chunked(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK, GemmCfg<0, 2>::B_CHUNKS,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if (rc != 0) return rc;
     return cta_group == 1 ? launch_gemm<0, 1>(stream, dev, a0, a0, b0, b0, p, max_ctas)
                           : launch_gemm<0, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
 }
@@ -251,9 +298,14 @@ int run_tf32(cudaStream_t stream, int dev, bool cplx, uint32_t M, uint32_t N, ui
     int rc;
     if ((rc = make_map(&a0, false, a_hi, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
     if ((rc = make_map(&a1, false, a_lo, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
-    if ((rc = make_map(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+    // the planes are padded to whole 32-float chunks (ldbw), so the one-load-per-stage form is always legal
+    p.b_chunked_map = 1;
+    const uint32_t chunks = (cta_group == 1) ? GemmCfg<1, 1>::B_CHUNKS : GemmCfg<1, 2>::B_CHUNKS;
+    if ((rc = make_map_b_chunked(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, chunks,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
-    if ((rc = make_map(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+    if ((rc = make_map_b_chunked(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, chunks,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
     return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
                           : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);

@@ -59,11 +59,27 @@ struct GemmParams {
     float alpha_re, alpha_im, beta_re, beta_im;
     int epi_mode;              // EpilogueMode
     int vec_d, vec_c;          // 1 if 16-byte vector access to D / C rows is legal
+    int b_chunked_map;         // 1: the B maps are 3-D (column, k, 128-byte chunk): one TMA fetches a whole stage
+                               // 0: 2-D maps, one TMA per 128-byte column chunk
     uint32_t tiles_m, tiles_n; // in units of (128*CTAS) x 256
     uint32_t group_m;          // rasterisation group height, in tiles
     unsigned* status;          // device word, may be nullptr
     unsigned long long wait_limit_ns;
+    // soft lockstep of the persistent CTAs (see g_wave_ticket)
+    unsigned sync_base;        // value of the ticket counter when this launch starts
+    unsigned sync_on;          // 0 = off
+    unsigned sync_limit_ns;    // how long a producer waits for the others before it goes on alone
 };
+
+// Ticket counter of the soft tile barrier.  All CTAs of a launch are resident at once (one per SM), and
+// they share A row slabs and B column slabs through L2 only while they walk K at the same pace; left
+// alone they drift apart and the slabs are fetched from HBM again and again.  So before a producer
+// starts loading its next tile it takes a ticket and waits -- for a bounded time, then it carries on
+// regardless -- until every worker has finished issuing its previous tile.  The barrier is a hint:
+// releasing early or late changes DRAM traffic, never results.  Every launch adds exactly n_tiles
+// tickets, so the host can hand each launch its starting value.
+__device__ unsigned g_wave_ticket;
+
 
 template <int KIND, int CTAS>
 struct GemmCfg {
@@ -270,9 +286,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             tma_prefetch_desc(&tmB0);
             if constexpr (KIND == 1) { tma_prefetch_desc(&tmA1); tma_prefetch_desc(&tmB1); }
             const uint32_t full_target = (CTAS == 2) ? map_to_cta(full_bar, 0) : full_bar;
-            uint32_t s = 0, ph = 0;
+            uint32_t s = 0, ph = 0, my_iter = 0;
             bool ok = true;
-            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
+            for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++my_iter) {
+                if (p.sync_on && leader && my_iter > 0) {
+                    atomicAdd(&g_wave_ticket, 1u);           // this worker has issued all loads of its previous tile
+                    const uint32_t done_before = min(n_tiles, my_iter * n_workers);   // tiles of earlier rounds
+                    const unsigned target = p.sync_base + done_before;
+                    const uint64_t t0 = global_timer_ns();
+                    while (int(*reinterpret_cast<volatile unsigned*>(&g_wave_ticket) - target) < 0) {
+                        if (global_timer_ns() - t0 > p.sync_limit_ns) break;      // soft: go on alone
+                    }
+                }
                 uint32_t tm, tn;
                 tile_coords(t, p, tm, tn);
                 const int32_t row0 = int32_t((tm * CTAS + cta_rank) * Cfg::BM);
@@ -295,17 +320,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         const uint32_t b_dst = stage + Cfg::NPL * Cfg::A_TILE + pl * Cfg::B_TILE;
                         if constexpr (CTAS == 2) tma_load_2d_pair(a_dst, ma, fb, k0, row0);
                         else tma_load_2d(a_dst, ma, fb, k0, row0);
+                        if (p.b_chunked_map) {
+                            // all B_CHUNKS chunks of this stage in one instruction: the issuing thread, not
+                            // the memory system, limits how fast stages can be refilled
+                            if constexpr (CTAS == 2) tma_load_3d_pair(b_dst, mb, fb, 0, k0, col0 / Cfg::CHUNK_N);
+                            else tma_load_3d(b_dst, mb, fb, 0, k0, col0 / Cfg::CHUNK_N);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < Cfg::B_CHUNKS; ++j) {
-                            if constexpr (CTAS == 2)
-                                tma_load_2d_pair(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
-                            else
-                                tma_load_2d(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
+                            for (int j = 0; j < Cfg::B_CHUNKS; ++j) {
+                                if constexpr (CTAS == 2)
+                                    tma_load_2d_pair(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
+                                else
+                                    tma_load_2d(b_dst + j * Cfg::B_CHUNK_BYTES, mb, fb, col0 + j * Cfg::CHUNK_N, k0);
+                            }
                         }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
+            if (p.sync_on && leader && my_iter > 0) atomicAdd(&g_wave_ticket, 1u);   // ticket of the last tile
             // tail: every stage this CTA filled has been released by the MMA side, so no
             // arrival (possibly from the peer CTA) can land after this CTA has exited
             if (ok) {
@@ -333,6 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             const uint32_t peer_accf = (CTAS == 2) ? map_to_cta(accf_bar, 1) : 0u;
             uint32_t s = 0, ph = 0, it = 0;          // `it` counts accumulation chains (chunks)
             bool ok = true;
+
             for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
                 for (uint32_t c = 0; c < n_chunks && ok; ++c, ++it) {
                     const uint32_t a = it & 1u, aph = (it >> 1) & 1u;

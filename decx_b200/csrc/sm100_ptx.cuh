@@ -79,21 +79,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// same, with cluster-scope acquire (needed when the arrival came from the peer CTA)
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait.  Returns false after `limit_ns` without completion: the caller then
 // records an error code and unwinds; no wait in these kernels spins for ever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
@@ -107,18 +92,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t polls = 0;
-    while (true) {
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (((++polls) & 63u) == 0u) {
-            if (global_timer_ns() - t0 > limit_ns) return false;
-        }
-    }
-}
-
 // ---------------------------------------------------------------------------
 // TMA (tiled, 2-D).  x = innermost coordinate; x * element size must be a
 // multiple of 16 bytes (every caller passes a multiple of the 128-byte box width).
@@ -145,6 +118,26 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
         " [%0], [%1, {%3, %4}], [%2];"
         :
         : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+// 3-D forms of the two loads above (x innermost, then y, then z)
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar,
+                                            int32_t x, int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* m,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 
