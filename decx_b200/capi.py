@@ -37,6 +37,8 @@ def _load():
     lib.decxb200_gemm_host_arena_bytes.argtypes = [ci, u32, u32, u32, ci]
     lib.decxb200_gemm_host.restype = ci
     lib.decxb200_gemm_host.argtypes = [ci, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
+    lib.decxb200_gemm_fp32_noalloc.restype = ci
+    lib.decxb200_gemm_fp32_noalloc.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp]
     pvp = ctypes.POINTER(ctypes.c_void_p)
     lib.decxb200_ipc_alloc.restype = ci
     lib.decxb200_ipc_alloc.argtypes = [sz, pvp]
@@ -62,6 +64,7 @@ lib = _load()
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
+    "decxb200_gemm_fp32_noalloc",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
 ]
@@ -70,6 +73,9 @@ EXPORTS = [
 def check(code):
     if code != 0:
         raise DecxB200Error(code, lib.decxb200_strerror(code).decode())
+
+
+NOALLOC_SCRATCH_BYTES = 16 << 20
 
 
 def workspace_bytes(dtype, M, N, K):

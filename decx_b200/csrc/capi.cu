@@ -536,6 +536,63 @@ int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K, c
                             workspace_bytes, status, 0, 0);
 }
 
+// ------------------------------------------------------------------------------------------
+// fp32 GEMM whose scratch is a fixed array inside the library (see the header for who needs it)
+// ------------------------------------------------------------------------------------------
+// Lives in every context that loads this module until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DECXB200_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address, so the
+// address each device gave the array is looked up once per device and kept here.
+void* g_noalloc_addr[MAX_DEVICES] = {nullptr};
+
+int noalloc_scratch_address(int dev, void** out) {
+    std::lock_guard<std::mutex> lk(g_dev_mutex);
+    if (g_noalloc_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);   // for the CURRENT device (= dev)
+        if (e != cudaSuccess) return int(e);
+        if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0) return DECXB200_EWORKSPACE;
+        g_noalloc_addr[dev] = ptr;
+    }
+    *out = g_noalloc_addr[dev];
+    return 0;
+}
+}  // namespace
+
+int decxb200_gemm_fp32_noalloc(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
+                               const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                               const void* alpha, const void* beta, unsigned* status) {
+    t_launches = 0;
+    int dev = 0, cta_group = 0;
+    int rc = check_common(DECXB200_FP32, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, cta_group, dev);
+    if (rc != 0) return rc;
+    const size_t need = decxb200_gemm_workspace_bytes(DECXB200_FP32, M, N, K);
+    if (need > size_t(DECXB200_NOALLOC_SCRATCH_BYTES)) return DECXB200_ETOOLARGE;
+    void* scratch = nullptr;
+    if ((rc = noalloc_scratch_address(dev, &scratch)) != 0) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    // The array still holds the planes of whichever call used it last.  The one-load-per-stage form of
+    // the B tensor map reads the padding columns of the B planes, which the split pass does not write:
+    // clear the part this call uses so that nothing stale (for instance NaN bit patterns) is ever read.
+    const cudaError_t ce = cudaMemsetAsync(scratch, 0, need, stream);
+    if (ce != cudaSuccess) return int(ce);
+    const Scalars sc = read_scalars(DECXB200_FP32, alpha, beta);
+    const uint64_t ldaw = round_up(K, 32), ldbw = round_up(N, 32);
+    const uint64_t a_bytes = round_up(uint64_t(M) * ldaw * 4, 256);
+    const uint64_t b_bytes = round_up(uint64_t(K) * ldbw * 4, 256);
+    uint8_t* w = static_cast<uint8_t*>(scratch);
+    float* a_hi = reinterpret_cast<float*>(w);
+    float* a_lo = reinterpret_cast<float*>(w + a_bytes);
+    float* b_hi = reinterpret_cast<float*>(w + 2 * a_bytes);
+    float* b_lo = reinterpret_cast<float*>(w + 2 * a_bytes + b_bytes);
+    if ((rc = prep_a(stream, false, A, lda, M, K, a_hi, a_lo, ldaw)) != 0) return rc;
+    if ((rc = prep_b(stream, false, B, ldb, K, N, b_hi, b_lo, ldbw)) != 0) return rc;
+    return run_tf32(stream, dev, false, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, C, ldc, D, ldd, sc, status,
+                    cta_group, 0);
+}
+
 int decxb200_ipc_alloc(size_t bytes, void** dptr) {
     if (dptr == nullptr || bytes == 0) return DECXB200_EINVAL;
     const cudaError_t e = cudaMalloc(dptr, bytes);   // a whole allocation: IPC handles name allocations

@@ -111,6 +111,37 @@ DECXB200_API int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t 
                                     void* arena, size_t arena_bytes, unsigned* status);
 
 /*
+ * fp32 GEMM for callers that must not allocate.  (No counterpart in the reference, whose GEMM always
+ * takes its scratch from the device memory pool.)
+ *
+ * Some code that wants an fp32 GEMM cannot obtain device scratch for it: a plug-in that runs inside a
+ * host application whose own allocator has already claimed the GPU's memory, a latency-critical loop
+ * that may not risk the implicit device synchronisation and the driver locks of cudaMalloc/cudaFree, or
+ * a module that is only ever handed finished input and output buffers.  For them this entry point keeps
+ * the scratch of the 3xTF32 path (the tf32 hi/lo planes of A and B) in a fixed array inside the library:
+ * DECXB200_NOALLOC_SCRATCH_BYTES of device memory, held by every GPU context that loads the library for
+ * as long as the process lives.  The caller passes only inputs and outputs; the call itself uses no
+ * cudaMalloc, cudaFree or any other allocating routine.
+ *
+ *   Same meaning as decxb200_gemm(DECXB200_FP32, ...): D = alpha * A * B + beta * C, device pointers,
+ *   asynchronous on `stream`, `status` optional.
+ *   Limit: decxb200_gemm_workspace_bytes(DECXB200_FP32, M, N, K) must not exceed
+ *   DECXB200_NOALLOC_SCRATCH_BYTES (for example 1024 x 1024 x 1024 fits exactly); larger problems return
+ *   DECXB200_ETOOLARGE and launch nothing.
+ *   First use: the first call on each device looks up the array's device address (with that device
+ *   current) and remembers it.  Make that first call during set-up, before any stream capture begins.
+ *   Sharing: every call on a device uses the same array, and the array keeps what the previous call
+ *   left in it; each call clears the part it is going to use before writing its planes.  Two calls that
+ *   overlap on the GPU (different streams, or different host threads without ordering) race on it:
+ *   order them on one stream or with events.
+ */
+#define DECXB200_NOALLOC_SCRATCH_BYTES (16u << 20)
+DECXB200_API int decxb200_gemm_fp32_noalloc(void* stream, uint32_t M, uint32_t N, uint32_t K,
+                                            const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                                            const void* C, uint64_t ldc, void* D, uint64_t ldd,
+                                            const void* alpha, const void* beta, unsigned* status);
+
+/*
  * Peer-visible device buffers for the row-sharded multi-GPU GEMM (one process per GPU).
  * The owner of the result allocates D with decxb200_ipc_alloc and exports a 64-byte handle;
  * every other rank opens it and passes `peer_ptr + its row offset` as the D argument of
