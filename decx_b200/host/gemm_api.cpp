@@ -1,0 +1,221 @@
+// de::blas::cuda::GEMM -- the four overloads of the drop-in.
+//
+// Reference flow (srcs/modules/BLAS/GEMM/CUDA/GEMM_LS.cu:62-109, 315-393): cast to the concrete matrices,
+// validate, take a pooled non-blocking stream and a blocking-sync event, re-construct dst, plan, launch the
+// chosen SIMT kernel, record + wait on the event, give stream and event back.  This file keeps that flow and
+// its error codes; "plan + launch" is one call into the C ABI (include/decx_b200.h), and the planner-owned
+// A-transpose scratch is replaced by the tf32-plane workspace, cached with the reference's 5 s lifespan.
+// Unlike the reference, a failed validation returns before anything is launched, and nothing calls exit().
+#include <cstring>
+
+#include "../../include/decx_b200.h"
+#include "internal.h"
+
+namespace {
+
+int abi_dtype(de::_DATA_TYPES_FLAGS_ t) {
+    switch (t) {
+        case de::_FP32_: return DECXB200_FP32;
+        case de::_FP16_: return DECXB200_FP16;
+        case de::_COMPLEX_F32_: return DECXB200_CPLXF;
+        default: return -1;
+    }
+}
+
+void fail(int code, const char* msg) { decx::err::set(de::GetLastError(), code, msg); }
+
+// alpha / beta as the accumulate type the C ABI wants (float, or {re, im})
+bool scalar_of(const de::Number& n, de::_DATA_TYPES_FLAGS_ t, float out[2]) {
+    if (n.Type() != int32_t(t)) return false;
+    out[1] = 0.f;
+    if (t == de::_FP32_) out[0] = n.get_data_ref<float>();
+    else if (t == de::_FP16_) out[0] = de::Half2Float(n.get_data_ref<de::Half>());
+    else {
+        out[0] = n.get_data_ref<de::CPf>().real;
+        out[1] = n.get_data_ref<de::CPf>().image;
+    }
+    return true;
+}
+
+void report_abi_error(int rc) {
+    if (rc == DECXB200_EALIGN || rc == DECXB200_EINVAL || rc == DECXB200_ETOOLARGE)
+        fail(de::DECX_FAIL_INVALID_PARAM, decxb200_strerror(rc));
+    else if (rc == DECXB200_EWORKSPACE)
+        fail(de::DECX_FAIL_CUDA_ALLOCATION, decxb200_strerror(rc));
+    else if (rc == DECXB200_EDRIVER)
+        fail(de::DECX_FAIL_CUDA_not_init, decxb200_strerror(rc));
+    else
+        fail(de::DECX_FAIL_CUDA_STREAM, decxb200_strerror(rc));
+}
+
+// scratch caches, created on first use and never destroyed (like the reference's planners they are owned by
+// the resource manager, which returns their memory after 5 idle seconds)
+decx::ScratchResource* workspace_cache() {
+    static decx::ScratchResource* r = new decx::ScratchResource(5.0);
+    return r;
+}
+decx::ScratchResource* arena_cache() {
+    static decx::ScratchResource* r = new decx::ScratchResource(5.0);
+    return r;
+}
+
+// one status word per device for the kernels' bounded waits, and a pinned host copy to read it back
+struct StatusWord {
+    decx::PtrInfo<void> dev;
+    unsigned* host = nullptr;
+};
+StatusWord* status_word(int device) {
+    static std::mutex mtx;
+    static StatusWord words[64];
+    std::lock_guard<std::mutex> lk(mtx);
+    if (device < 0 || device >= 64) return nullptr;
+    StatusWord& w = words[device];
+    if (w.dev.ptr == nullptr) {
+        if (decx::alloc::_device_malloc(&w.dev, sizeof(unsigned), true, nullptr) != 0) return nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void**>(&w.host), sizeof(unsigned), cudaHostAllocDefault) != cudaSuccess) {
+            cudaGetLastError();
+            decx::alloc::_device_dealloc(&w.dev);
+            return nullptr;
+        }
+        *w.host = 0;
+    }
+    return &w;
+}
+
+struct DeviceScope {   // makes `device` current for the call, restores the caller's device afterwards
+    int prev = 0;
+    bool switched = false;
+    explicit DeviceScope(int device) {
+        cudaGetDevice(&prev);
+        if (device >= 0 && device != prev) { cudaSetDevice(device); switched = true; }
+    }
+    ~DeviceScope() { if (switched) cudaSetDevice(prev); }
+};
+
+void gemm_device(de::GPU_Matrix& A_, de::GPU_Matrix& B_, de::GPU_Matrix* C_, de::GPU_Matrix& dst_,
+                 const de::Number* alpha, const de::Number* beta) {
+    decx::_GPU_Matrix* A = dynamic_cast<decx::_GPU_Matrix*>(&A_);
+    decx::_GPU_Matrix* B = dynamic_cast<decx::_GPU_Matrix*>(&B_);
+    decx::_GPU_Matrix* C = C_ ? dynamic_cast<decx::_GPU_Matrix*>(C_) : nullptr;
+    decx::_GPU_Matrix* dst = dynamic_cast<decx::_GPU_Matrix*>(&dst_);
+    if (!decx::cuda::_is_CUDA_init()) return fail(de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first");
+    if (A == nullptr || B == nullptr || dst == nullptr || (C_ && C == nullptr) || !A->_init || !B->_init || (C && !C->_init))
+        return fail(de::DECX_FAIL_CLASS_NOT_INIT, "error: The class is not initialized");
+    // validation of the reference (large_squares/common/cuda_GEMM_LS_planner.cu:229-258) plus C's extents,
+    // which its CUDA path forgets and its CPU path checks (cpu_GEMM_config.cxx:218-224)
+    if (A->Width() != B->Height()) return fail(de::DECX_FAIL_DimsNotMatching, "error: Dim(s) is(are) not equal to each other");
+    if (A->Type() != B->Type() || (C && C->Type() != A->Type()))
+        return fail(de::DECX_FAIL_TYPE_MOT_MATCH, "error: The types of the two objects are not equal");
+    const int dt = abi_dtype(A->Type());
+    if (dt < 0) return fail(de::DECX_FAIL_UNSUPPORTED_TYPE, "error: The data type is not supported by GEMM on this path");
+    if (C && (C->Width() != B->Width() || C->Height() != A->Height()))
+        return fail(de::DECX_FAIL_DimsNotMatching, "error: Dim(s) is(are) not equal to each other");
+    float a[2] = {1.f, 0.f}, b[2] = {0.f, 0.f};
+    if (C) {
+        if (!scalar_of(*alpha, A->Type(), a) || !scalar_of(*beta, A->Type(), b))
+            return fail(de::DECX_FAIL_TYPE_MOT_MATCH, "error: The types of the two objects are not equal");
+    }
+    if (dst == A || dst == B) return fail(de::DECX_FAIL_INVALID_PARAM, "error: dst must not be one of the factors");
+    if (B->_device != A->_device || (C && C->_device != A->_device))
+        return fail(de::DECX_FAIL_INVALID_PARAM, "error: the matrices live on different devices");
+
+    DeviceScope scope(A->_device);
+    decx::cuda_stream* S = decx::cuda::get_cuda_stream_ptr(cudaStreamNonBlocking);
+    if (S == nullptr) return fail(de::DECX_FAIL_CUDA_STREAM, "error: Fail to access cuda stream");
+    decx::cuda_event* E = decx::cuda::get_cuda_event_ptr(cudaEventBlockingSync);
+    if (E == nullptr) {
+        S->detach();
+        return fail(de::DECX_FAIL_CUDA_EVENT, "error: Fail to access cuda event");
+    }
+    const uint32_t M = A->Height(), N = B->Width(), K = A->Width();
+    dst->re_construct(A->Type(), N, M, S);
+    StatusWord* sw = status_word(A->_device);
+    if (!dst->_init || sw == nullptr) {
+        S->detach();
+        E->detach();
+        return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
+    }
+    const size_t need = decxb200_gemm_workspace_bytes(dt, M, N, K);
+    void* ws = nullptr;
+    if (need) {
+        ws = workspace_cache()->lock(need, A->_device);
+        if (ws == nullptr) {
+            S->detach();
+            E->detach();
+            return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
+        }
+    }
+    const int rc = decxb200_gemm(dt, S->get_raw_stream_ref(), M, N, K, A->Mat.ptr, A->Pitch(), B->Mat.ptr, B->Pitch(),
+                                 C ? C->Mat.ptr : nullptr, C ? C->Pitch() : 0, dst->Mat.ptr, dst->Pitch(), C ? a : nullptr,
+                                 C ? b : nullptr, ws, need, static_cast<unsigned*>(sw->dev.ptr));
+    if (rc == 0)
+        cudaMemcpyAsync(sw->host, sw->dev.ptr, sizeof(unsigned), cudaMemcpyDeviceToHost, S->get_raw_stream_ref());
+    E->event_record(S);
+    E->synchronize();                       // the API is synchronous, as in the reference (GEMM_LS.cu:102-103)
+    if (need) workspace_cache()->unlock();
+    S->detach();
+    E->detach();
+    if (rc != 0) return report_abi_error(rc);
+    if (*sw->host != 0) {
+        char msg[96];
+        snprintf(msg, sizeof(msg), "error: a bounded wait inside the GEMM kernel expired (code 0x%x)", *sw->host);
+        *sw->host = 0;
+        cudaMemset(sw->dev.ptr, 0, sizeof(unsigned));
+        return fail(de::DECX_FAIL_CUDA_STREAM, msg);
+    }
+}
+
+void gemm_host(de::Matrix& A_, de::Matrix& B_, de::Matrix* C_, de::Matrix& dst_) {
+    decx::_Matrix* A = dynamic_cast<decx::_Matrix*>(&A_);
+    decx::_Matrix* B = dynamic_cast<decx::_Matrix*>(&B_);
+    decx::_Matrix* C = C_ ? dynamic_cast<decx::_Matrix*>(C_) : nullptr;
+    decx::_Matrix* dst = dynamic_cast<decx::_Matrix*>(&dst_);
+    if (!decx::cuda::_is_CUDA_init()) return fail(de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first");
+    if (A == nullptr || B == nullptr || dst == nullptr || (C_ && C == nullptr) || !A->_init || !B->_init || (C && !C->_init))
+        return fail(de::DECX_FAIL_CLASS_NOT_INIT, "error: The class is not initialized");
+    if (A->Width() != B->Height()) return fail(de::DECX_FAIL_DimsNotMatching, "error: Dim(s) is(are) not equal to each other");
+    if (A->Type() != B->Type() || (C && C->Type() != A->Type()))
+        return fail(de::DECX_FAIL_TYPE_MOT_MATCH, "error: The types of the two objects are not equal");
+    const int dt = abi_dtype(A->Type());
+    if (dt < 0) return fail(de::DECX_FAIL_UNSUPPORTED_TYPE, "error: The data type is not supported by GEMM on this path");
+    if (C && (C->Width() != B->Width() || C->Height() != A->Height()))
+        return fail(de::DECX_FAIL_DimsNotMatching, "error: Dim(s) is(are) not equal to each other");
+    if (dst == A || dst == B) return fail(de::DECX_FAIL_INVALID_PARAM, "error: dst must not be one of the factors");
+    const uint32_t M = A->Height(), N = B->Width(), K = A->Width();
+    dst->re_construct(A->Type(), N, M);
+    if (!dst->_init) return fail(de::DECX_FAIL_ALLOCATION, "error: Fail to allocate memory on RAM");
+    int device = 0;
+    cudaGetDevice(&device);
+    StatusWord* sw = status_word(device);
+    const size_t need = decxb200_gemm_host_arena_bytes(dt, M, N, K, C ? 1 : 0);
+    void* arena = arena_cache()->lock(need, device);
+    if (arena == nullptr || sw == nullptr) {
+        if (arena != nullptr) arena_cache()->unlock();
+        return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
+    }
+    const float one[2] = {1.f, 0.f};
+    const int rc = decxb200_gemm_host(dt, M, N, K, A->data, A->Pitch(), B->data, B->Pitch(), C ? C->data : nullptr,
+                                      C ? C->Pitch() : 0, dst->data, dst->Pitch(), C ? one : nullptr, C ? one : nullptr,
+                                      arena, need, static_cast<unsigned*>(sw->dev.ptr));
+    arena_cache()->unlock();
+    if (rc == DECXB200_EKERNEL) {
+        cudaMemset(sw->dev.ptr, 0, sizeof(unsigned));
+        return fail(de::DECX_FAIL_CUDA_STREAM, decxb200_strerror(rc));
+    }
+    if (rc != 0) return report_abi_error(rc);
+}
+
+}  // namespace
+
+void de::blas::cuda::GEMM(de::GPU_Matrix& A, de::GPU_Matrix& B, de::GPU_Matrix& dst) {
+    gemm_device(A, B, nullptr, dst, nullptr, nullptr);
+}
+
+void de::blas::cuda::GEMM(de::GPU_Matrix& A, de::GPU_Matrix& B, de::GPU_Matrix& C, de::GPU_Matrix& dst,
+                          const de::Number alpha, const de::Number beta) {
+    gemm_device(A, B, &C, dst, &alpha, &beta);
+}
+
+void de::blas::cuda::GEMM(de::Matrix& A, de::Matrix& B, de::Matrix& dst) { gemm_host(A, B, nullptr, dst); }
+
+void de::blas::cuda::GEMM(de::Matrix& A, de::Matrix& B, de::Matrix& C, de::Matrix& dst) { gemm_host(A, B, &C, dst); }

@@ -1,0 +1,13 @@
+// Umbrella header of the drop-in (the reference's srcs/includes/DECX.h pulls in every module; this one
+// pulls in what the dense-GEMM path needs).
+#ifndef DECX_B200_PUBLIC_DECX_H_
+#define DECX_B200_PUBLIC_DECX_H_
+#include "DECX/basic.h"
+#include "DECX/classes/type_info.h"
+#include "DECX/classes/class_utils.h"
+#include "DECX/classes/DecxNumber.h"
+#include "DECX/classes/Matrix.h"
+#include "DECX/classes/GPU_Matrix.h"
+#include "DECX/classes/decx_memcpy.h"
+#include "DECX/BLAS/BLAS.h"
+#endif

@@ -1,0 +1,203 @@
+// GPU test of the C++ drop-in, written the way a DECX user program is written (compare the reference's
+// samples/Matrix_Multiplication/MatMul.cpp): InitCuda, Create*MatrixRef(type, width, height), fill through
+// ptr<T>(row, col), de::Memcpy, de::blas::cuda::GEMM, de::Memcpy back, look at de::GetLastError().
+// Results are checked against an fp64 triple loop (fp32 for fp16) with the path's metric
+//   max |D - Dref| / (|A row| * |B column|)  <=  1e-5 (fp32, complex)   1e-2 (fp16).
+#include <cmath>
+#include <complex>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "DECX.h"
+
+static int g_fail = 0;
+#define CHECK(c) do { if (!(c)) { std::printf("FAIL %s:%d  %s\n", __FILE__, __LINE__, #c); ++g_fail; } } while (0)
+
+static uint32_t g_seed = 1;
+static float rnd() {   // U[-1, 1)
+    g_seed = g_seed * 1664525u + 1013904223u;
+    return float(int32_t(g_seed >> 8) - (1 << 23)) / float(1 << 23);
+}
+
+template <typename T> struct Ops;
+template <> struct Ops<float> {
+    static constexpr de::_DATA_TYPES_FLAGS_ type = de::_FP32_;
+    typedef double wide;
+    static float make() { return rnd(); }
+    static wide up(float x) { return x; }
+    static double mag(wide x) { return std::fabs(x); }
+    static de::Number num(double re, double) { return de::Number(float(re)); }
+    static wide scal(double re, double) { return re; }
+    static constexpr double tol = 1e-5;
+};
+template <> struct Ops<de::CPf> {
+    static constexpr de::_DATA_TYPES_FLAGS_ type = de::_COMPLEX_F32_;
+    typedef std::complex<double> wide;
+    static de::CPf make() { return de::CPf(rnd(), rnd()); }
+    static wide up(de::CPf x) { return wide(x.real, x.image); }
+    static double mag(wide x) { return std::abs(x); }
+    static de::Number num(double re, double im) { return de::Number(de::CPf(float(re), float(im))); }
+    static wide scal(double re, double im) { return wide(re, im); }
+    static constexpr double tol = 1e-5;
+};
+template <> struct Ops<de::Half> {
+    static constexpr de::_DATA_TYPES_FLAGS_ type = de::_FP16_;
+    typedef double wide;
+    static de::Half make() { return de::Float2Half(rnd() * 0.5f); }
+    static wide up(de::Half x) { return de::Half2Float(x); }
+    static double mag(wide x) { return std::fabs(x); }
+    static de::Number num(double re, double) { return de::Number(de::Float2Half(float(re))); }
+    static wide scal(double re, double) { return re; }
+    static constexpr double tol = 1e-2;
+};
+
+// M x N x K problem through the device-matrix overloads (fused when `fused`), and through the host-matrix ones
+template <typename T>
+static void run_case(uint32_t M, uint32_t N, uint32_t K, bool fused, bool host_overload) {
+    typedef Ops<T> O;
+    typedef typename O::wide W;
+    de::Matrix& A = de::CreateMatrixRef(O::type, K, M);
+    de::Matrix& B = de::CreateMatrixRef(O::type, N, K);
+    de::Matrix& C = de::CreateMatrixRef(O::type, N, M);
+    de::Matrix& D = de::CreateMatrixRef(O::type, N, M);
+    for (uint32_t i = 0; i < M; ++i) for (uint32_t k = 0; k < K; ++k) *A.ptr<T>(i, k) = O::make();
+    for (uint32_t k = 0; k < K; ++k) for (uint32_t j = 0; j < N; ++j) *B.ptr<T>(k, j) = O::make();
+    for (uint32_t i = 0; i < M; ++i) for (uint32_t j = 0; j < N; ++j) *C.ptr<T>(i, j) = O::make();
+    const double ar = host_overload ? 1.0 : 0.75, ai = host_overload ? 0.0 : -0.5;
+    const double br = host_overload ? 1.0 : -1.25, bi = host_overload ? 0.0 : 0.5;
+    const bool cplx = (O::type == de::_COMPLEX_F32_);
+    de::ResetLastError();
+    if (host_overload) {
+        if (fused) de::blas::cuda::GEMM(A, B, C, D); else de::blas::cuda::GEMM(A, B, D);
+    } else {
+        de::GPU_Matrix& dA = de::CreateGPUMatrixRef(O::type, K, M);
+        de::GPU_Matrix& dB = de::CreateGPUMatrixRef(O::type, N, K);
+        de::GPU_Matrix& dC = de::CreateGPUMatrixRef(O::type, N, M);
+        de::GPU_Matrix& dD = de::CreateGPUMatrixRef();                    // shaped by GEMM
+        de::Memcpy(A, dA, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(K, M), de::DECX_MEMCPY_H2D);
+        de::Memcpy(B, dB, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(N, K), de::DECX_MEMCPY_H2D);
+        de::Memcpy(C, dC, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(N, M), de::DECX_MEMCPY_H2D);
+        if (fused) de::blas::cuda::GEMM(dA, dB, dC, dD, O::num(ar, cplx ? ai : 0), O::num(br, cplx ? bi : 0));
+        else de::blas::cuda::GEMM(dA, dB, dD);
+        CHECK(dD.Width() == N && dD.Height() == M && dD.Type() == O::type);
+        de::Memcpy(D, dD, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(N, M), de::DECX_MEMCPY_D2H);
+        dA.release(); dB.release(); dC.release(); dD.release();
+    }
+    CHECK(de::GetLastError()->error_type == de::DECX_SUCCESS);
+    if (de::GetLastError()->error_type != de::DECX_SUCCESS) std::printf("  DH: %s\n", de::GetLastError()->error_string);
+    std::vector<double> rn(M, 0.0), cn(N, 0.0);
+    for (uint32_t i = 0; i < M; ++i) { for (uint32_t k = 0; k < K; ++k) rn[i] += std::norm(O::up(*A.ptr<T>(i, k))); rn[i] = std::sqrt(rn[i]); }
+    for (uint32_t j = 0; j < N; ++j) { for (uint32_t k = 0; k < K; ++k) cn[j] += std::norm(O::up(*B.ptr<T>(k, j))); cn[j] = std::sqrt(cn[j]); }
+    const W alpha = fused ? O::scal(ar, cplx ? ai : 0) : O::scal(1, 0), beta = fused ? O::scal(br, cplx ? bi : 0) : O::scal(0, 0);
+    double worst = 0.0;
+    for (uint32_t i = 0; i < M; ++i)
+        for (uint32_t j = 0; j < N; ++j) {
+            W acc = O::scal(0, 0);
+            for (uint32_t k = 0; k < K; ++k) acc += O::up(*A.ptr<T>(i, k)) * O::up(*B.ptr<T>(k, j));
+            const W ref = alpha * acc + beta * O::up(*C.ptr<T>(i, j));
+            const double m = O::mag(O::up(*D.ptr<T>(i, j)) - ref) / (rn[i] * cn[j]);
+            if (!(m <= worst)) worst = m;
+        }
+    std::printf("  %s %ux%ux%u %s %s: metric %.3e (limit %.0e)\n", cplx ? "cplxf" : (O::type == de::_FP16_ ? "fp16" : "fp32"),
+                M, N, K, fused ? "fused" : "plain", host_overload ? "host-matrix" : "device-matrix", worst, O::tol);
+    CHECK(worst <= O::tol);
+    A.release(); B.release(); C.release(); D.release();
+}
+
+// the reference sample's known answer: A = (j, 0), B = (i, 0), C = (1e6, 1e6) -> (sum i^2 + 1e6, 1e6)
+static void sample_known_answer() {
+    const uint32_t W = 1013, H = 1077, L = 1005;
+    de::Matrix& A = de::CreateMatrixRef(de::_COMPLEX_F32_, L, H);
+    de::Matrix& B = de::CreateMatrixRef(de::_COMPLEX_F32_, W, L);
+    de::Matrix& C = de::CreateMatrixRef(de::_COMPLEX_F32_, W, H);
+    de::Matrix& D = de::CreateMatrixRef(de::_COMPLEX_F32_, W, H);
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < L; ++j) *A.ptr<de::CPf>(i, j) = de::CPf(float(j), 0.f);
+    for (uint32_t i = 0; i < L; ++i) for (uint32_t j = 0; j < W; ++j) *B.ptr<de::CPf>(i, j) = de::CPf(float(i), 0.f);
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) *C.ptr<de::CPf>(i, j) = de::CPf(1e6f, 1e6f);
+    de::GPU_Matrix& dA = de::CreateGPUMatrixRef(de::_COMPLEX_F32_, L, H);
+    de::GPU_Matrix& dB = de::CreateGPUMatrixRef(de::_COMPLEX_F32_, W, L);
+    de::GPU_Matrix& dC = de::CreateGPUMatrixRef(de::_COMPLEX_F32_, W, H);
+    de::GPU_Matrix& dD = de::CreateGPUMatrixRef(de::_COMPLEX_F32_, W, H);
+    de::Memcpy(A, dA, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(L, H), de::DECX_MEMCPY_H2D);
+    de::Memcpy(B, dB, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, L), de::DECX_MEMCPY_H2D);
+    de::Memcpy(C, dC, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_H2D);
+    de::blas::cuda::GEMM(dA, dB, dC, dD, de::Number(de::CPf(1.f, 0.f)), de::Number(de::CPf(1.f, 0.f)));
+    de::Memcpy(D, dD, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_D2H);
+    double expect = 1e6;
+    for (uint32_t i = 0; i < L; ++i) expect += double(i) * i;
+    double worst = 0;
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) {
+        worst = std::fmax(worst, std::fabs(D.ptr<de::CPf>(i, j)->real - expect) / expect);
+        worst = std::fmax(worst, std::fabs(D.ptr<de::CPf>(i, j)->image - 1e6) / expect);
+    }
+    std::printf("  sample known answer: worst relative deviation %.3e\n", worst);
+    CHECK(worst < 2e-6);
+}
+
+static void error_paths() {
+    de::GPU_Matrix& a = de::CreateGPUMatrixRef(de::_FP32_, 8, 4);     // 4 x 8
+    de::GPU_Matrix& b = de::CreateGPUMatrixRef(de::_FP32_, 5, 9);     // 9 x 5: inner extents differ
+    de::GPU_Matrix& h = de::CreateGPUMatrixRef(de::_FP16_, 5, 8);
+    de::GPU_Matrix& d = de::CreateGPUMatrixRef();
+    de::ResetLastError();
+    de::blas::cuda::GEMM(a, b, d);
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_DimsNotMatching);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(a, h, d);
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_TYPE_MOT_MATCH);
+    de::GPU_Matrix& b2 = de::CreateGPUMatrixRef(de::_FP32_, 5, 8);
+    de::GPU_Matrix& c2 = de::CreateGPUMatrixRef(de::_FP32_, 5, 4);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(a, b2, c2, d, de::Number(1.0f), de::Number(de::Float2Half(1.f)));   // beta of another type
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_TYPE_MOT_MATCH);
+    de::GPU_Matrix& i32 = de::CreateGPUMatrixRef(de::_INT32_, 8, 8);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(i32, i32, d);
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_UNSUPPORTED_TYPE);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(a, b2, a);                                   // dst aliases a factor
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_INVALID_PARAM);
+    // Memcpy range check: {x = column, y = row}
+    de::Matrix& hm = de::CreateMatrixRef(de::_FP32_, 8, 4);
+    de::ResetLastError();
+    de::DH r = de::Memcpy(hm, a, de::Point2D(4, 0), de::Point2D(0, 0), de::Point2D(8, 4), de::DECX_MEMCPY_H2D);
+    CHECK(r.error_type == de::DECX_FAIL_MEMCPY_OVERRANGED);
+    // sub-block copy lands where it should
+    for (int i = 0; i < 4; ++i) for (int j = 0; j < 8; ++j) *hm.ptr<float>(i, j) = float(10 * i + j);
+    de::Matrix& back = de::CreateMatrixRef(de::_FP32_, 8, 4);
+    r = de::Memcpy(hm, a, de::Point2D(2, 1), de::Point2D(1, 0), de::Point2D(3, 2), de::DECX_MEMCPY_H2D);
+    CHECK(r.error_type == de::DECX_SUCCESS);
+    de::Memcpy(back, a, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(8, 4), de::DECX_MEMCPY_D2H);
+    CHECK(*back.ptr<float>(0, 1) == 12.f && *back.ptr<float>(1, 3) == 24.f && *back.ptr<float>(0, 0) == 0.f);
+    // dst is grown on demand and keeps its block when the next result is smaller
+    de::GPU_Matrix& big = de::CreateGPUMatrixRef(de::_FP32_, 64, 64);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(big, big, d);
+    CHECK(d.Width() == 64 && d.Height() == 64 && de::GetLastError()->error_type == de::DECX_SUCCESS);
+    de::blas::cuda::GEMM(a, b2, d);
+    CHECK(d.Width() == 5 && d.Height() == 4 && de::GetLastError()->error_type == de::DECX_SUCCESS);
+}
+
+int main() {
+    de::InitCPUInfo();
+    de::InitCuda();
+    if (de::GetLastError()->error_type != de::DECX_SUCCESS) { std::printf("no CUDA device\n"); return 2; }
+    const uint32_t shapes[][3] = {{1, 1, 1}, {17, 5, 9}, {129, 257, 65}, {300, 200, 150}, {513, 130, 260}};
+    for (auto& s : shapes)
+        for (int fused = 0; fused < 2; ++fused) {
+            run_case<float>(s[0], s[1], s[2], fused, false);
+            run_case<de::Half>(s[0], s[1], s[2], fused, false);
+            run_case<de::CPf>(s[0], s[1], s[2], fused, false);
+        }
+    for (int fused = 0; fused < 2; ++fused) {
+        run_case<float>(2300, 140, 90, fused, true);      // several row blocks in the host-matrix pipeline
+        run_case<de::Half>(300, 136, 72, fused, true);
+        run_case<de::CPf>(260, 70, 33, fused, true);
+    }
+    sample_known_answer();
+    error_paths();
+    de::cuda::DECX_CUDA_exit();
+    if (g_fail == 0) std::printf("gemm_api: all checks passed\n");
+    return g_fail == 0 ? 0 : 1;
+}
