@@ -41,6 +41,21 @@ def test_drop_in_exports_the_reference_symbols():
         assert sym in out, f"{sym} is not exported"
 
 
+REF_INC = "/root/reference/srcs/includes"
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_INC), reason="reference headers not mounted")
+def test_program_built_against_reference_headers_runs_on_the_drop_in(tmp_path):
+    """ABI check: a program compiled with the reference's public headers links and runs against libDECX_b200."""
+    host, csrc = os.path.join(ROOT, "decx_b200", "host"), os.path.join(ROOT, "decx_b200", "csrc")
+    exe = str(tmp_path / "abi_probe")
+    subprocess.run(["g++", "-std=c++17", "-include", "cstdint", "-I", REF_INC,
+                    os.path.join(ROOT, "tests", "cpp_abi", "abi_probe.cxx"), "-o", exe, "-L", host, "-lDECX_b200",
+                    "-L", csrc, "-ldecx_b200", f"-Wl,-rpath,{host}", f"-Wl,-rpath,{csrc}"], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and "abi probe ok" in r.stdout
+
+
 @pytest.mark.gpu
 def test_gemm_api_gpu():
     r = _run("gemm_api")
