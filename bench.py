@@ -423,7 +423,9 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu
 # captures summarised under profiles/ (None = not captured for that configuration)
-TRAFFIC_BYTES_PER_LAUNCH = {}
+# fp16 16384^3: 8.84 GB read + 0.54 GB written (profiles/gemm_tcgen05_f16_16384x16384x16384.md); config 5 has
+# 4x the row slabs at the same N and K, so 4x the traffic per launch; fp32 8192^3 from its own capture.
+TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 9.38e9, ("cfg5", 1): 37.5e9, ("cfg2", 1): 4.83e9}
 
 if __name__ == "__main__":
     main()
