@@ -87,6 +87,15 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
 template <int KIND, int CTAS>
 int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                 const CUtensorMap& b1, GemmParams p, int max_ctas) {
+    // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
+    // that is what makes the stores efficient when D lives in another GPU's memory; DECXB200_TMA_STORE=0 disables
+    static const int tma_store_env = [] { const char* e = getenv("DECXB200_TMA_STORE"); return e ? atoi(e) : 1; }();
+    CUtensorMap dmap = a0;
+    p.d_tma = 0;
+    if (tma_store_env && p.vec_d) {
+        const bool f16 = (KIND == 0);
+        if (make_map(&dmap, f16, p.D, p.M, p.N, p.ldd, f16 ? 64 : 32, 32) == 0) p.d_tma = 1;
+    }
     using Cfg = GemmCfg<KIND, CTAS>;
     auto kern = gemm_tcgen05_kernel<KIND, CTAS>;
     DeviceInfo& di = g_dev[dev];
@@ -142,7 +151,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, p);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
     return 0;

@@ -59,6 +59,8 @@ struct GemmParams {
     float alpha_re, alpha_im, beta_re, beta_im;
     int epi_mode;              // EpilogueMode
     int vec_d, vec_c;          // 1 if 16-byte vector access to D / C rows is legal
+    int d_tma;                 // 1: D is written by TMA bulk stores from a shared-memory staging tile (128-byte rows,
+                               //    edges clipped in hardware); 0: predicated per-thread stores
     int b_chunked_map;         // 1: the B maps are 3-D (column, k, 128-byte chunk): one TMA fetches a whole stage
                                // 0: 2-D maps, one TMA per 128-byte column chunk
     uint32_t tiles_m, tiles_n; // in units of (128*CTAS) x 256
@@ -103,7 +105,8 @@ struct GemmCfg {
     static constexpr int EPI_WARPS = PROMOTE ? 8 : 4;
     static constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // accumulator columns per epilogue thread
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-    static constexpr int SMEM_BYTES = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int STAGING = EPI_WARPS * 4096;      // per epilogue warp: 32 rows x 128 bytes of output
+    static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
 };
 
@@ -124,10 +127,16 @@ __device__ __forceinline__ void report(const GemmParams& p, unsigned code) {
 }
 
 template <int KIND>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, float (&acc)[32]) {
-    // acc holds the fp32 accumulators of columns col0 .. col0+31 of `row` (clobbered)
-    const bool has_c = (p.C != nullptr);
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, float (&acc)[32],
+                                            uint32_t stage_row = 0, uint32_t unit0 = 0) {
+    // acc holds the fp32 accumulators of columns col0 .. col0+31 of `row` (clobbered).
+    // stage_row == 0: write them to D (the caller guarantees row < M).
+    // stage_row != 0: shared-memory address of this thread's 128-byte row of the warp's staging tile; the
+    //   values go there (16-byte units unit0.., 128-byte swizzle) and a TMA store writes the tile later.  Rows
+    //   at or beyond M are staged too (TMA drops them) but never read C.
+    const bool has_c = (p.C != nullptr) && (row < p.M);
     const uint32_t ncols = min(32u, p.N - col0);
+    const uint32_t sw = (stage_row >> 7) & 7u;               // row index within the 8-row swizzle atom
 
     if constexpr (KIND == 0) {
         __half* drow = reinterpret_cast<__half*>(p.D) + size_t(row) * p.ldd + col0;
@@ -157,7 +166,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
                 for (int i = 0; i < 32; ++i) acc[i] *= p.alpha_re;
             }
         }
-        if (ncols == 32 && p.vec_d) {
+        if (stage_row != 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(acc[q * 8 + 2 * j], acc[q * 8 + 2 * j + 1]);
+                st_shared_v4(stage_row + (((unit0 + q) ^ sw) << 4), o.x, o.y, o.z, o.w);
+            }
+        } else if (ncols == 32 && p.vec_d) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint4 o;
@@ -213,7 +231,13 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
                 }
             }
         }
-        if (ncols == 32 && p.vec_d) {
+        if (stage_row != 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                st_shared_v4(stage_row + (((unit0 + q) ^ sw) << 4), __float_as_uint(acc[4 * q]),
+                             __float_as_uint(acc[4 * q + 1]), __float_as_uint(acc[4 * q + 2]),
+                             __float_as_uint(acc[4 * q + 3]));
+        } else if (ncols == 32 && p.vec_d) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 reinterpret_cast<float4*>(drow)[q] =
@@ -230,14 +254,15 @@ template <int KIND, int CTAS>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
     using Cfg = GemmCfg<KIND, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle pattern
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE;
+    const uint32_t staging_base = smem_base + STAGES * Cfg::STAGE;   // 1024-byte aligned: 4 KB per epilogue warp
+    const uint32_t bar_base = staging_base + Cfg::STAGING;
     const uint32_t full_bar = bar_base;                      // STAGES x 8 B
     const uint32_t empty_bar = bar_base + 8 * STAGES;        // STAGES x 8 B
     const uint32_t accf_bar = bar_base + 16 * STAGES;        // 2 x 8 B  accumulator full
@@ -430,6 +455,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
         const uint32_t colpart = (warp - 2u) >> 2;           // which EPI_COLS-wide slice of the 256 columns
         const uint32_t acce_target = (CTAS == 2) ? map_to_cta(acce_bar, 0) : acce_bar;
+        const uint32_t stage_warp = staging_base + (warp - 2u) * 4096u;   // this warp's 32 x 128-byte staging tile
+        const uint32_t stage_row = p.d_tma ? stage_warp + lane * 128u : 0u;
+        constexpr uint32_t BOX_COLS = 128 / ((KIND == 0) ? 2 : 4);        // output columns per 128-byte row
+        if (p.d_tma && lane == 0) tma_prefetch_desc(&tmD);
+        // TMA drops rows at or beyond M exactly, but it was seen to clip the column edge in 16-byte units, so a box
+        // that crosses an edge N which is not 16-byte aligned is written by predicated per-thread stores instead
+        const bool ragged_n = ((p.N * ((KIND == 0) ? 2u : 4u)) & 15u) != 0u;
         uint32_t it = 0;                                     // accumulation chains seen so far
         bool ok = true;
         for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
@@ -467,15 +499,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         else mbar_arrive(acce_bar + 8 * a);
                     }
                 }
-                if (ok && row < p.M) {
+                if (ok && (p.d_tma || row < p.M)) {
+                    const uint32_t warp_row0 = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32;
 #pragma unroll
                     for (int q = 0; q < Cfg::EPI_COLS / 32; ++q) {
                         const uint32_t col0 = colbase + q * 32;
-                        if (col0 < p.N) {
+                        if (col0 < p.N) {                    // uniform across the warp
                             float part[32];
 #pragma unroll
                             for (int i = 0; i < 32; ++i) part[i] = sum[q * 32 + i];
-                            store_chunk<KIND>(p, row, col0, part);
+                            if (p.d_tma && !(ragged_n && col0 + BOX_COLS > p.N)) {
+                                if (lane == 0) bulk_wait_read_all();     // the previous box has left the staging tile
+                                __syncwarp();
+                                store_chunk<KIND>(p, row, col0, part, stage_row, 0);
+                                fence_proxy_async_smem();
+                                __syncwarp();
+                                if (lane == 0 && warp_row0 < p.M) {
+                                    tma_store_2d(&tmD, stage_warp, int32_t(col0), int32_t(warp_row0));
+                                    bulk_commit_group();
+                                }
+                            } else if (row < p.M) {
+                                store_chunk<KIND>(p, row, col0, part);
+                            }
                         }
                     }
                 }
@@ -498,7 +543,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     float acc[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(v[i]);
-                    if (row < p.M) store_chunk<KIND>(p, row, col0, acc);
+                    const uint32_t box_col0 = col0 - (c & (BOX_COLS / 32 - 1)) * 32;
+                    if (p.d_tma && !(ragged_n && box_col0 + BOX_COLS > p.N)) {
+                        // two 32-column chunks fill one 64-column (128-byte) box of fp16 output
+                        const uint32_t half = c & (BOX_COLS / 32 - 1);
+                        if (half == 0) {
+                            if (lane == 0) bulk_wait_read_all();         // the previous box has left the staging tile
+                            __syncwarp();
+                        }
+                        store_chunk<KIND>(p, row, col0, acc, stage_row, half * 4);
+                        if (half == BOX_COLS / 32 - 1 || col0 + 32 >= p.N) {
+                            const uint32_t warp_row0 = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32;
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0 && warp_row0 < p.M) {
+                                tma_store_2d(&tmD, stage_warp, int32_t(col0 - half * 32), int32_t(warp_row0));
+                                bulk_commit_group();
+                            }
+                        }
+                    } else if (row < p.M) {
+                        store_chunk<KIND>(p, row, col0, acc);
+                    }
                 }
                 tc_fence_before_sync();
                 __syncwarp();
@@ -510,6 +575,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             }
         }
     }
+
+    if (warp >= 2 && lane == 0 && p.d_tma) bulk_wait_all();   // this thread's output boxes are in memory
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
