@@ -152,7 +152,7 @@ def cpu_baseline(workload, bounded_rows=1024):
             "seconds": best, "host_cpus": os.cpu_count()}
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank, world, emit):
     """--impl reference: the reference's CPU implementation of the path on this host's cores."""
     if rank != 0:
         return
@@ -178,7 +178,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
@@ -231,8 +231,18 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    # Libraries (NCCL's version banner, torchrun notices) may write to stdout; the contract is ONE JSON line
+    # there.  Everything else goes to stderr: fd 1 is pointed at stderr and the line is written to the saved fd.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+    def emit(line):
+        real_stdout.write(json.dumps(line) + "\n")
+        real_stdout.flush()
+
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, emit)
         return
 
     import torch
@@ -420,7 +430,7 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu
