@@ -5,8 +5,11 @@
 The reference is single-GPU (its sources hold no cudaSetDevice, peer copy or collective), so this
 layer is new surface on top of the same per-GPU GEMM.  One step is:
 
-  1. B travels from the owner to every rank in column panels: the owner packs panel j into a
-     contiguous K x Np buffer and NCCL broadcasts it (NVLink / NVSwitch) on a communication stream;
+  1. B travels from the owner to every rank in column panels on a communication stream: the owner packs
+     panel j into a contiguous K x Np buffer; then either one NCCL broadcast ("broadcast"), or -- the
+     default for more than two ranks, because an 8-rank ncclBroadcast only reaches ~150 GB/s here -- the
+     owner scatters one row block of the panel to each rank and an all-gather completes it everywhere
+     ("scatter_allgather": every link of the NVSwitch fabric carries a share, the owner sends the panel once);
   2. as soon as panel j has landed in this rank's own HBM, the rank's GEMM for that panel runs on the
      compute stream, D[rows of this rank, panel j] = A_r . B[:, panel j]  (its TMA loads read local
      memory only, none of them uses cluster multicast), while panel j+1 is still in flight;
@@ -74,7 +77,8 @@ class ShardedGemm:
     GEMM in CPU tests only; on a GPU the C ABI is called and there is no other path.
     """
 
-    def __init__(self, M, N, K, dtype, group=None, owner=0, panels=4, gather=None, device=None, gemm_fn=None):
+    def __init__(self, M, N, K, dtype, group=None, owner=0, panels=4, gather=None, device=None, gemm_fn=None,
+                 reserve_sms=None, bcast=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -84,6 +88,11 @@ class ShardedGemm:
         if not self.on_gpu and gemm_fn is None:
             raise RuntimeError("ShardedGemm computes on CUDA devices only (a host GEMM can only be injected by tests)")
         self.gemm_fn = gemm_fn
+        self.bcast = bcast or ("scatter_allgather" if self.world > 2 else "broadcast")
+        # SMs left free for the communication kernels while a GEMM runs: the GEMM is persistent (one CTA per
+        # SM for its whole duration), so without this NCCL's broadcast of the next panel cannot get an SM
+        # until the GEMM ends and the pipeline becomes broadcast-bound.
+        self.reserve_sms = (8 if self.world > 1 else 0) if reserve_sms is None else reserve_sms
         self.gather = gather or ("peer" if self.on_gpu and self.world > 1 else "collective")
         self.rows = row_ranges(M, self.world)
         self.row0, self.nrows = self.rows[self.rank]
@@ -109,6 +118,8 @@ class ShardedGemm:
             need = max((capi.workspace_bytes(self._dt, max(self.nrows, 1), w, K) for _, w in self.panels), default=0)
             self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
             self._ws_bytes = need
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            self._max_ctas = max(2, sms - self.reserve_sms) if self.reserve_sms else 0
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.events = [torch.cuda.Event() for _ in self.panels]
         if self.gather == "peer":
@@ -174,7 +185,26 @@ class ShardedGemm:
                                     None, 0, d_ptr, self.N,
                                     ws_ptr=self.workspace.data_ptr() if self._ws_bytes else None,
                                     ws_bytes=self._ws_bytes, status_ptr=self.status.data_ptr(),
-                                    stream=torch.cuda.current_stream(self.device).cuda_stream)
+                                    stream=torch.cuda.current_stream(self.device).cuda_stream,
+                                    max_ctas=self._max_ctas)
+
+    def _send_panel(self, j):
+        """Make panel j of B present on every rank (issued on the communication stream)."""
+        c0, w = self.panels[j]
+        buf = self.Bp[j]
+        if self.is_owner:
+            buf.copy_(self.B[:, c0:c0 + w])
+        if self.bcast == "scatter_allgather" and self.K % self.world == 0:
+            rows = self.K // self.world
+            mine = buf[self.rank * rows:(self.rank + 1) * rows]
+            if self.is_owner:
+                chunks = [buf[r * rows:(r + 1) * rows] for r in range(self.world)]
+                dist.scatter(mine, scatter_list=chunks, src=self.owner, group=self.group)
+            else:
+                dist.scatter(mine, src=self.owner, group=self.group)
+            dist.all_gather_into_tensor(buf, mine, group=self.group)     # in place: `mine` is this rank's slice
+        else:
+            dist.broadcast(buf, src=self.owner, group=self.group)
 
     def step(self):
         """Broadcast B, multiply, gather on the owner.  Asynchronous on a GPU: the caller synchronises."""
@@ -188,10 +218,8 @@ class ShardedGemm:
                 cur = torch.cuda.current_stream(self.device)
                 self.comm_stream.wait_stream(cur)
                 with torch.cuda.stream(self.comm_stream):
-                    for j, (c0, w) in enumerate(self.panels):
-                        if self.is_owner:
-                            self.Bp[j].copy_(self.B[:, c0:c0 + w])
-                        dist.broadcast(self.Bp[j], src=self.owner, group=self.group)
+                    for j in range(len(self.panels)):
+                        self._send_panel(j)
                         self.events[j].record(self.comm_stream)
                 for j in range(len(self.panels)):
                     cur.wait_event(self.events[j])
@@ -200,10 +228,8 @@ class ShardedGemm:
                     self._collect()
                 dist.barrier(group=self.group)      # every rank's rows have reached the owner
         else:
-            for j, (c0, w) in enumerate(self.panels):
-                if self.is_owner:
-                    self.Bp[j].copy_(self.B[:, c0:c0 + w])
-                dist.broadcast(self.Bp[j], src=self.owner, group=self.group)
+            for j in range(len(self.panels)):
+                self._send_panel(j)
                 self._panel_gemm(j)
             self._collect()
             dist.barrier(group=self.group)

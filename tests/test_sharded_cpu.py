@@ -53,13 +53,13 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, out):
+def _worker(rank, world, port, M, N, K, bcast, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         def host_gemm(A, Bp, D):          # stands in for the CUDA GEMM in this CPU-only test
             D.copy_((A.double() @ Bp.double()).float())
-        sg = ShardedGemm(M, N, K, torch.float32, owner=0, panels=3, device="cpu", gemm_fn=host_gemm)
+        sg = ShardedGemm(M, N, K, torch.float32, owner=0, panels=3, device="cpu", gemm_fn=host_gemm, bcast=bcast)
         g = torch.Generator().manual_seed(1)
         A = torch.rand((M, K), generator=g) * 2 - 1
         B = torch.rand((K, N), generator=g) * 2 - 1
@@ -75,13 +75,14 @@ def _worker(rank, world, port, M, N, K, out):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("bcast", ["broadcast", "scatter_allgather"])
 @pytest.mark.parametrize("shape", [(700, 600, 50), (256, 300, 33)])
-def test_two_rank_schedule_over_gloo(shape):
+def test_two_rank_schedule_over_gloo(shape, bcast):
     M, N, K = shape
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, M, N, K, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, M, N, K, bcast, q)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

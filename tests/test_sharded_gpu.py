@@ -24,7 +24,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, dtype_name, gather, out):
+def _worker(rank, world, port, M, N, K, dtype_name, gather, bcast, out):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -41,7 +41,7 @@ def _worker(rank, world, port, M, N, K, dtype_name, gather, out):
         else:
             mk = lambda r, c: (torch.rand((r, c), device=dev, generator=g) * 2 - 1).to(dtype)
         A, B = mk(M, K), mk(K, N)                     # same seed on every rank: identical full inputs
-        sg = ShardedGemm(M, N, K, dtype, owner=0, panels=3, gather=gather, device=dev)
+        sg = ShardedGemm(M, N, K, dtype, owner=0, panels=3, gather=gather, device=dev, bcast=bcast)
         sg.A.copy_(A[sg.row0:sg.row0 + sg.nrows])
         if sg.is_owner:
             sg.B.copy_(B)
@@ -64,12 +64,13 @@ def _worker(rank, world, port, M, N, K, dtype_name, gather, out):
 @pytest.mark.parametrize("dtype_name,shape", [("float16", (2048, 1536, 512)), ("float32", (1100, 700, 300)),
                                               ("complex64", (600, 520, 130))])
 def test_sharded_equals_single_gpu(dtype_name, shape, gather):
+    bcast = "scatter_allgather" if gather == "peer" else "broadcast"      # both ways of moving B get covered
     world = min(torch.cuda.device_count(), 4)
     M, N, K = shape
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, dtype_name, gather, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, dtype_name, gather, bcast, q)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
