@@ -10,6 +10,10 @@ layer is new surface on top of the same per-GPU GEMM.  One step is:
      default for more than two ranks, because an 8-rank ncclBroadcast only reaches ~150 GB/s here -- the
      owner scatters one row block of the panel to each rank and an all-gather completes it everywhere
      ("scatter_allgather": every link of the NVSwitch fabric carries a share, the owner sends the panel once);
+     or "p2p": the same scatter + all-gather pattern done by the copy engines -- the panel buffers live in
+     symmetric memory, every rank PULLS its row block from the owner and then the other blocks from the
+     ranks that hold them, ordered by stream-level signals, so no communication kernel competes with the
+     persistent GEMM for SMs;
   2. as soon as panel j has landed in this rank's own HBM, the rank's GEMM for that panel runs on the
      compute stream, D[rows of this rank, panel j] = A_r . B[:, panel j]  (its TMA loads read local
      memory only, none of them uses cluster multicast), while panel j+1 is still in flight;
@@ -101,9 +105,14 @@ class ShardedGemm:
         dev = self.device
         self.A = torch.empty((max(self.nrows, 1), K), dtype=dtype, device=dev)[: self.nrows]
         self.B = torch.empty((K, N), dtype=dtype, device=dev) if self.is_owner else None
-        if self.world > 1:
+        self._hdl = None
+        if self.world > 1 and self.bcast == "p2p" and (not self.on_gpu or K % self.world != 0):
+            self.bcast = "broadcast"
+        if self.world > 1 and self.bcast == "p2p":
+            self._setup_symmetric_panels()
+        if self.world > 1 and self._hdl is None:
             self.Bp = [torch.empty((K, w), dtype=dtype, device=dev) for _, w in self.panels]
-        else:
+        elif self.world == 1:
             self.Bp = [self.B]
         self.launches = 0
         self._peer_base = None
@@ -128,6 +137,45 @@ class ShardedGemm:
             self.D = torch.empty((M, N), dtype=dtype, device=dev) if self.is_owner else None
             self.D_local = self.D[self.row0:self.row0 + self.nrows] if self.is_owner else \
                 torch.empty((max(self.nrows, 1), N), dtype=dtype, device=dev)[: self.nrows]
+
+    # ------------------------------------------------------------------ B panels in symmetric memory ("p2p")
+    def _setup_symmetric_panels(self):
+        """All panels of B in one symmetric allocation; every rank can address every other rank's copy."""
+        import sys
+        try:
+            import torch.distributed._symmetric_memory as symm
+            total = self.K * self.N
+            self._bsym = symm.empty(total, dtype=self.dtype, device=self.device)
+            grp = self.group if self.group is not None else dist.group.WORLD
+            self._hdl = symm.rendezvous(self._bsym, group=grp)
+            self._poff, off = [], 0
+            for _, w in self.panels:
+                self._poff.append(off)
+                off += self.K * w
+            self.Bp = [self._bsym[o:o + self.K * w].view(self.K, w) for o, (_, w) in zip(self._poff, self.panels)]
+            self._peer = [self._hdl.get_buffer(r, (total,), self.dtype, 0) for r in range(self.world)]
+        except Exception as e:       # symmetric memory not available on this system: NCCL broadcast instead
+            print(f"decx_b200.sharded: symmetric memory unavailable ({type(e).__name__}: {e}); using ncclBroadcast",
+                  file=sys.stderr)
+            self._hdl = None
+            self.bcast = "broadcast"
+
+    def _send_panel_p2p(self, j):
+        c0, w = self.panels[j]
+        buf, rows = self.Bp[j], self.K // self.world
+        blk, base = rows * w, self._poff[j]
+        if self.is_owner:
+            buf.copy_(self.B[:, c0:c0 + w])
+        self._hdl.barrier(channel=0)                       # the owner's copy of the panel is complete
+        if not self.is_owner:
+            lo = base + self.rank * blk
+            self._bsym[lo:lo + blk].copy_(self._peer[self.owner][lo:lo + blk])
+        self._hdl.barrier(channel=1)                       # every rank holds its own row block
+        if not self.is_owner:
+            for d in range(1, self.world):
+                src = (self.rank + d) % self.world         # stagger the sources over the ranks
+                lo = base + src * blk
+                self._bsym[lo:lo + blk].copy_(self._peer[src][lo:lo + blk])
 
     # ------------------------------------------------------------------ peer-visible D on the owner
     def _setup_peer_d(self):
@@ -158,6 +206,8 @@ class ShardedGemm:
             torch.cuda.synchronize(self.device)
         if dist.is_initialized() and self.world > 1:
             dist.barrier(group=self.group)
+        self._peer = None
+        self._hdl = None
         if self._peer_base is not None:
             self._capi.lib.decxb200_ipc_close(self._peer_base)
             self._peer_base = None
@@ -190,6 +240,8 @@ class ShardedGemm:
 
     def _send_panel(self, j):
         """Make panel j of B present on every rank (issued on the communication stream)."""
+        if self.bcast == "p2p":
+            return self._send_panel_p2p(j)
         c0, w = self.panels[j]
         buf = self.Bp[j]
         if self.is_owner:
