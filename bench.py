@@ -218,7 +218,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
-    ap.add_argument("--panels", type=int, default=4, help="column panels of B in the sharded path")
+    ap.add_argument("--panels", default="ramp", help="column panels of B in the sharded path: a count or 'ramp'")
+    ap.add_argument("--bcast", default=None, choices=[None, "p2p", "broadcast", "scatter_allgather"])
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--kernel-only", action="store_true",
@@ -282,7 +283,8 @@ def main():
         return float(t.item())
 
     # ------------------------------------------------------------ device-resident measurement
-    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=args.panels, gather=args.gather, device=device)
+    panels = args.panels if args.panels == "ramp" else int(args.panels)
+    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast)
     if sg.nrows:
         sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
     if sg.is_owner:
@@ -398,7 +400,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": ARITH[dtype], "data": "synthetic (seeded, generated on the device)",
         "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
-                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels, gather={sg.gather}" if world > 1 else ""),
+                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, gather={sg.gather}" if world > 1 else ""),
                    "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30)},
         "pct_of_peak": {"value": 100 * value / (world * peak), "denominator_tflops": world * peak,
                         "which": f"{pk['source']} bf16 burst x {world} GPU(s)" + ("" if dtype == "float16" else ", /2 for TF32, /3 for 3xTF32"),

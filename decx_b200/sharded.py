@@ -49,7 +49,30 @@ def row_ranges(M, world, align=ROW_ALIGN):
 
 
 def panel_plan(N, panels, align=COL_ALIGN):
-    """[(first_col, cols)] of the column panels of B: `panels` near-equal multiples of `align`."""
+    """[(first_col, cols)] of the column panels of B.
+
+    `panels` is a count (near-equal multiples of `align`), a list of widths, or "ramp": a small first panel
+    (N/16) so that the first GEMM can start early, then 3N/16, then quarters -- nothing hides the arrival of
+    the first panel, everything after it travels while a GEMM runs."""
+    if panels == "ramp":
+        units = (N + align - 1) // align
+        if units < 16:
+            return panel_plan(N, min(4, units), align)
+        first, second = max(1, units // 16), max(1, 3 * units // 16)
+        rest = units - first - second
+        q, extra = divmod(rest, 3)
+        widths = [first, second] + [q + (1 if i < extra else 0) for i in range(3)]
+        panels = [w * align for w in widths if w > 0]
+    if isinstance(panels, (list, tuple)):
+        out, c = [], 0
+        for w in panels:
+            w = min(int(w), N - c)
+            if w > 0:
+                out.append((c, w))
+                c += w
+        if c < N:
+            out.append((c, N - c))
+        return out
     blocks = (N + align - 1) // align
     panels = max(1, min(panels, blocks))
     base, extra = divmod(blocks, panels)
@@ -81,7 +104,7 @@ class ShardedGemm:
     GEMM in CPU tests only; on a GPU the C ABI is called and there is no other path.
     """
 
-    def __init__(self, M, N, K, dtype, group=None, owner=0, panels=4, gather=None, device=None, gemm_fn=None,
+    def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
                  reserve_sms=None, bcast=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -92,11 +115,11 @@ class ShardedGemm:
         if not self.on_gpu and gemm_fn is None:
             raise RuntimeError("ShardedGemm computes on CUDA devices only (a host GEMM can only be injected by tests)")
         self.gemm_fn = gemm_fn
-        self.bcast = bcast or ("scatter_allgather" if self.world > 2 else "broadcast")
+        self.bcast = bcast or ("p2p" if self.on_gpu else "broadcast")
         # SMs left free for the communication kernels while a GEMM runs: the GEMM is persistent (one CTA per
         # SM for its whole duration), so without this NCCL's broadcast of the next panel cannot get an SM
         # until the GEMM ends and the pipeline becomes broadcast-bound.
-        self.reserve_sms = (8 if self.world > 1 else 0) if reserve_sms is None else reserve_sms
+        self._reserve_arg = reserve_sms
         self.gather = gather or ("peer" if self.on_gpu and self.world > 1 else "collective")
         self.rows = row_ranges(M, self.world)
         self.row0, self.nrows = self.rows[self.rank]
@@ -127,6 +150,10 @@ class ShardedGemm:
             need = max((capi.workspace_bytes(self._dt, max(self.nrows, 1), w, K) for _, w in self.panels), default=0)
             self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
             self._ws_bytes = need
+            # "p2p" moves B with the copy engines (its signal kernels are one tiny CTA): nothing to reserve;
+            # NCCL broadcasts need SMs of their own or the pipeline becomes broadcast-bound
+            self.reserve_sms = self._reserve_arg if self._reserve_arg is not None else \
+                (0 if (self.world == 1 or self.bcast == "p2p") else 16)
             sms = torch.cuda.get_device_properties(dev).multi_processor_count
             self._max_ctas = max(2, sms - self.reserve_sms) if self.reserve_sms else 0
             self.comm_stream = torch.cuda.Stream(device=dev)
