@@ -35,7 +35,7 @@ constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
     unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
-    bool attr_set[2][2] = {{false, false}, {false, false}};
+    bool attr_set[2][2][2] = {};
     int max_pairs[2] = {0, 0};
 };
 DeviceInfo g_dev[MAX_DEVICES];
@@ -84,7 +84,7 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
-template <int KIND, int CTAS>
+template <int KIND, int CTAS, int NACC = 1>
 int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                 const CUtensorMap& b1, GemmParams p, int max_ctas) {
     // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
@@ -96,8 +96,8 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
         const bool f16 = (KIND == 0);
         if (make_map(&dmap, f16, p.D, p.M, p.N, p.ldd, f16 ? 64 : 32, 32) == 0) p.d_tma = 1;
     }
-    using Cfg = GemmCfg<KIND, CTAS>;
-    auto kern = gemm_tcgen05_kernel<KIND, CTAS>;
+    using Cfg = GemmCfg<KIND, CTAS, NACC>;
+    auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC>;
     DeviceInfo& di = g_dev[dev];
     {
         std::lock_guard<std::mutex> lk(g_dev_mutex);
@@ -105,14 +105,14 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
             cudaError_t e = cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess) return int(e);
         }
-        if (!di.attr_set[KIND][CTAS - 1]) {
+        if (!di.attr_set[KIND][CTAS - 1][NACC - 1]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
             if (e != cudaSuccess) return int(e);
-            di.attr_set[KIND][CTAS - 1] = true;
+            di.attr_set[KIND][CTAS - 1][NACC - 1] = true;
         }
     }
     p.tiles_m = uint32_t((uint64_t(p.M) + Cfg::BM * CTAS - 1) / (Cfg::BM * CTAS));
-    p.tiles_n = uint32_t((uint64_t(p.N) + Cfg::BN - 1) / Cfg::BN);
+    p.tiles_n = uint32_t((uint64_t(p.N) + Cfg::BN_TILE - 1) / Cfg::BN_TILE);
     const uint64_t tiles = uint64_t(p.tiles_m) * p.tiles_n;
     if (tiles > 0xFFFFFFFFull) return DECXB200_ETOOLARGE;
     uint32_t workers = uint32_t(di.sm_count / CTAS);
@@ -120,7 +120,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     if (workers == 0) workers = 1;
     if (tiles < workers) workers = uint32_t(tiles);
     // group height: balance the A rows and B columns the concurrently running tiles touch
-    uint32_t g = (CTAS == 1) ? 16 : 8;
+    uint32_t g = (CTAS == 1) ? 16 : (NACC == 2 ? 12 : 8);
     if (const char* e = getenv("DECXB200_GROUP_M")) {       // tuning override
         const int v = atoi(e);
         if (v > 0) g = uint32_t(v);
@@ -273,10 +273,29 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
     CUtensorMap a0, b0;
     int rc;
     if ((rc = make_map(&a0, true, A, M, K, lda, C1::BK, C1::BM)) != 0) return rc;
+    // Two accumulators per tile (256 x 512 per CTA pair) when K is long enough to hide the unoverlapped epilogue
+    // and there are at least two rounds of such tiles; DECXB200_NACC=1|2 overrides.
+    int nacc = 1;
+    if (cta_group == 2) {
+        static const int nacc_env = [] { const char* e = getenv("DECXB200_NACC"); return e ? atoi(e) : 0; }();
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        // rounds of the persistent grid with either tile; a wide tile is two plain tiles of work at ~8 % less time
+        const uint64_t pairs = uint64_t(sms > 0 ? sms : 148) / 2;
+        const uint64_t rows256 = (uint64_t(M) + 255) / 256;
+        const uint64_t plain = rows256 * ((uint64_t(N) + 255) / 256), wide = rows256 * ((uint64_t(N) + 511) / 512);
+        const double t_plain = double((plain + pairs - 1) / pairs);
+        const double t_wide = double((wide + pairs - 1) / pairs) * 2.0 * 0.92;
+        nacc = (K >= 2048 && t_wide < t_plain) ? 2 : 1;
+        if (nacc_env == 1 || nacc_env == 2) nacc = nacc_env;
+    }
     // one 3-D load per stage when reading the last column chunk at full width stays inside B's rows
     p.b_chunked_map = ((N % C1::CHUNK_N) == 0 || ldb >= round_up(N, C1::CHUNK_N)) ? 1 : 0;
     if (!p.b_chunked_map) {
         rc = make_map(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK);
+    } else if (nacc == 2) {
+        rc = make_map_b_chunked(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK, GemmCfg<0, 2, 2>::B_CHUNKS,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
     } else if (cta_group == 1) {
         rc = make_map_b_chunked(&b0, true, B, K, N, ldb, C1::CHUNK_N, C1::BK, GemmCfg<0, 1>::B_CHUNKS,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
@@ -285,6 +304,7 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc != 0) return rc;
+    if (nacc == 2) return launch_gemm<0, 2, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
     return cta_group == 1 ? launch_gemm<0, 1>(stream, dev, a0, a0, b0, b0, p, max_ctas)
                           : launch_gemm<0, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
 }

@@ -30,6 +30,13 @@
 //         loads its own 128 rows of A and its own 128 columns of B (no multicast), the
 //         pair's leader issues the MMAs, each CTA keeps its 128 x 256 accumulator rows.
 //
+// NACC 2  (fp16 pairs only) the pair computes 256 x 512: two accumulators share every A tile, which
+//         cuts the operand traffic from L2 from 64 to 48 bytes per clock and SM -- the 256 x 256 tile
+//         sits at ~70 % of what the L2 can deliver without multicast and stalls on it.  CTA r loads
+//         the contiguous columns [512 t + 256 r, +256); accumulator h multiplies columns
+//         [.. + 128 h, +128) of both CTAs.  Both TMEM accumulators belong to one tile, so the epilogue
+//         (eight warps, four per accumulator) no longer overlaps the next tile's MMAs: used for long K.
+//
 // Ragged M/N/K: tensor maps carry the logical extents, so out-of-range parts of a box
 // are zero-filled by TMA; stores are predicated.  No host-side padding.
 // Every wait is bounded: on time-out the role writes a code to *status and unwinds.
@@ -83,13 +90,15 @@ struct GemmParams {
 __device__ unsigned g_wave_ticket;
 
 
-template <int KIND, int CTAS>
+template <int KIND, int CTAS, int NACC = 1>
 struct GemmCfg {
+    static_assert(NACC == 1 || (NACC == 2 && KIND == 0 && CTAS == 2), "two accumulators per tile: fp16 CTA pairs only");
     static constexpr int ELEM = (KIND == 0) ? 2 : 4;
     static constexpr int NPL = (KIND == 0) ? 1 : 2;       // operand planes (hi, lo)
     static constexpr int BM = 128;                        // rows per CTA
-    static constexpr int BN = 256;                        // UMMA N
-    static constexpr int BN_LOAD = BN / CTAS;             // columns of B this CTA loads
+    static constexpr int BN = 256;                        // UMMA N = columns of one accumulator
+    static constexpr int BN_TILE = BN * NACC;             // columns of one tile (NACC accumulators share each A tile)
+    static constexpr int BN_LOAD = BN_TILE / CTAS;        // columns of B this CTA loads per stage
     static constexpr int BK = 128 / ELEM;                 // one 128-byte swizzle row of K
     static constexpr int UMMA_K = 32 / ELEM;
     static constexpr int CHUNK_N = 128 / ELEM;            // B columns per 128-byte row
@@ -102,8 +111,9 @@ struct GemmCfg {
     static constexpr int TMEM_COLS = 512;                 // two 256-column accumulators
     static constexpr bool PROMOTE = (KIND == 1);          // chunked TMEM chains summed in registers
     static constexpr int CHUNK_KB = 4;                    // k-blocks per TMEM chain when PROMOTE
-    static constexpr int EPI_WARPS = PROMOTE ? 8 : 4;
-    static constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // accumulator columns per epilogue thread
+    static constexpr int EPI_WARPS = PROMOTE ? 8 : 4 * NACC;
+    static constexpr int EPI_COLS = PROMOTE ? BN / 2 : BN;   // accumulator columns per epilogue thread
+    static constexpr int ACC_ARRIVALS = (EPI_WARPS / NACC) * CTAS;   // epilogue warps (of the pair) per accumulator
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int STAGING = EPI_WARPS * 4096;      // per epilogue warp: 32 rows x 128 bytes of output
     static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -250,12 +260,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
     }
 }
 
-template <int KIND, int CTAS>
-__global__ void __launch_bounds__(GemmCfg<KIND, CTAS>::THREADS, 1)
+template <int KIND, int CTAS, int NACC>
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
-    using Cfg = GemmCfg<KIND, CTAS>;
+    using Cfg = GemmCfg<KIND, CTAS, NACC>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
@@ -291,7 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(accf_bar + 8 * a, 1);
-            mbar_init(acce_bar + 8 * a, Cfg::EPI_WARPS * CTAS);
+            mbar_init(acce_bar + 8 * a, Cfg::ACC_ARRIVALS);
         }
         fence_mbar_init();
     }
@@ -326,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 uint32_t tm, tn;
                 tile_coords(t, p, tm, tn);
                 const int32_t row0 = int32_t((tm * CTAS + cta_rank) * Cfg::BM);
-                const int32_t col0 = int32_t(tn * Cfg::BN + cta_rank * Cfg::BN_LOAD);
+                const int32_t col0 = int32_t(tn * Cfg::BN_TILE + cta_rank * Cfg::BN_LOAD);
                 for (uint32_t kb = 0; kb < n_kb; ++kb) {
                     if (!mbar_wait_bounded(empty_bar + 8 * s, ph ^ 1u, limit)) {
                         report(p, KS_TIMEOUT_PRODUCER);
@@ -394,8 +404,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 
             for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
                 for (uint32_t c = 0; c < n_chunks && ok; ++c, ++it) {
-                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
-                    if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
+                    // NACC 1: chains alternate between the two TMEM accumulators; NACC 2: a tile owns both
+                    const uint32_t a = (NACC == 2) ? 0u : (it & 1u);
+                    const uint32_t aph = (NACC == 2) ? (it & 1u) : ((it >> 1) & 1u);
+                    bool freed = mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit);
+                    if (NACC == 2 && freed) freed = mbar_wait_bounded(acce_bar + 8, aph ^ 1u, limit);
+                    if (!freed) {
                         report(p, KS_TIMEOUT_MMA_ACC);
                         ok = false;
                         break;
@@ -416,8 +430,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
                             const uint32_t acc_flag = ((kb - c * chunk_kb) | uint32_t(k)) ? 1u : 0u;
                             if constexpr (KIND == 0) {
-                                umma_ss<0, CTAS>(d_tmem, smem_desc_at(DESC_A, a0 + k * A_KSTEP),
-                                                 smem_desc_at(DESC_B, b0 + k * B_KSTEP), Cfg::IDESC, acc_flag);
+                                const uint64_t da = smem_desc_at(DESC_A, a0 + k * A_KSTEP);
+#pragma unroll
+                                for (int h = 0; h < NACC; ++h)      // accumulator h: this CTA's chunks [2h, 2h+2) when NACC = 2
+                                    umma_ss<0, CTAS>(d_tmem + h * Cfg::BN, da,
+                                                     smem_desc_at(DESC_B, b0 + h * (Cfg::B_TILE / NACC) + k * B_KSTEP),
+                                                     Cfg::IDESC, acc_flag);
                             } else {
                                 const uint64_t a_hi = smem_desc_at(DESC_A, a0 + k * A_KSTEP);
                                 const uint64_t a_lo = smem_desc_at(DESC_A, a0 + Cfg::A_TILE + k * A_KSTEP);
@@ -434,15 +452,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
                     if (ok) {
-                        umma_commit<CTAS>(accf_bar + 8 * a);              // chain complete
-                        if constexpr (CTAS == 2) umma_commit<CTAS>(peer_accf + 8 * a);
+#pragma unroll
+                        for (int h = 0; h < NACC; ++h) {
+                            umma_commit<CTAS>(accf_bar + 8 * (a + h));    // chain complete
+                            if constexpr (CTAS == 2) umma_commit<CTAS>(peer_accf + 8 * (a + h));
+                        }
                     }
                 }
             }
             // tail: both accumulators drained by every epilogue warp (of both CTAs)
             if (ok) {
-                for (int i = 0; i < 2; ++i, ++it) {
-                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t a = (NACC == 2) ? uint32_t(i) : (it & 1u);
+                    const uint32_t aph = (NACC == 2) ? (it & 1u) : ((it >> 1) & 1u);
+                    if (NACC == 1) ++it;
                     if (!mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit)) {
                         report(p, KS_TIMEOUT_TAIL);
                         break;
@@ -525,7 +548,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     }
                 }
             } else {
-                const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                // NACC 1: tiles alternate between the accumulators; NACC 2: warps 2..5 drain accumulator 0,
+                // warps 6..9 accumulator 1 of every tile
+                const uint32_t a = (NACC == 2) ? colpart : (it & 1u);
+                const uint32_t aph = (NACC == 2) ? (it & 1u) : ((it >> 1) & 1u);
                 if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
                     if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
                     ok = false;
@@ -535,7 +561,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 const uint32_t taddr = tmem_base + a * Cfg::BN + ((quarter * 32u) << 16);
 #pragma unroll 1
                 for (uint32_t c = 0; c < Cfg::EPI_COLS / 32; ++c) {
-                    const uint32_t col0 = colbase + c * 32;
+                    // accumulator column 32c -> matrix column.  NACC 2: columns 0..127 of accumulator h come from
+                    // CTA 0's B columns [128h, +128) of the tile, columns 128..255 from CTA 1's (256 further on)
+                    const uint32_t col0 = (NACC == 2) ? tn * Cfg::BN_TILE + ((c * 32) >> 7) * 256 + a * 128 + ((c * 32) & 127)
+                                                      : colbase + c * 32;
                     if (col0 >= p.N) break;                  // uniform across the warp
                     uint32_t v[32];
                     tmem_ld_32x32(taddr + c * 32, v);
