@@ -39,6 +39,13 @@ def _load():
     lib.decxb200_gemm_host.argtypes = [ci, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
     lib.decxb200_gemm_fp32_noalloc.restype = ci
     lib.decxb200_gemm_fp32_noalloc.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp]
+    lib.decxb200_gemm_fp16_panels.restype = ci
+    lib.decxb200_gemm_fp16_panels.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32,
+                                              ctypes.POINTER(u32), vp, ctypes.c_uint, ci]
+    lib.decxb200_copy2d_async.restype = ci
+    lib.decxb200_copy2d_async.argtypes = [vp, vp, sz, vp, sz, sz, sz]
+    lib.decxb200_write_flag_async.restype = ci
+    lib.decxb200_write_flag_async.argtypes = [vp, vp, ctypes.c_uint]
     pvp = ctypes.POINTER(ctypes.c_void_p)
     lib.decxb200_ipc_alloc.restype = ci
     lib.decxb200_ipc_alloc.argtypes = [sz, pvp]
@@ -65,6 +72,7 @@ EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
     "decxb200_gemm_fp32_noalloc",
+    "decxb200_gemm_fp16_panels", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
 ]

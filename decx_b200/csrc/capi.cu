@@ -115,6 +115,18 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     p.tiles_n = uint32_t((uint64_t(p.N) + Cfg::BN_TILE - 1) / Cfg::BN_TILE);
     const uint64_t tiles = uint64_t(p.tiles_m) * p.tiles_n;
     if (tiles > 0xFFFFFFFFull) return DECXB200_ETOOLARGE;
+    if (p.panel_flags == nullptr) {
+        p.n_panels = 1;
+        p.panel_end[0] = p.tiles_n;
+    } else {
+        // the caller gave panel ends in columns: they must fall on tile boundaries (the last one is N)
+        for (uint32_t i = 0; i < p.n_panels; ++i) {
+            const uint32_t cols = p.panel_end[i];
+            if (i + 1 < p.n_panels && (cols % Cfg::BN_TILE) != 0) return DECXB200_EINVAL;
+            p.panel_end[i] = (cols + Cfg::BN_TILE - 1) / Cfg::BN_TILE;
+        }
+        if (p.panel_end[p.n_panels - 1] != p.tiles_n) return DECXB200_EINVAL;
+    }
     uint32_t workers = uint32_t(di.sm_count / CTAS);
     if (max_ctas > 0 && uint32_t(max_ctas / CTAS) < workers) workers = uint32_t(max_ctas / CTAS);
     if (workers == 0) workers = 1;
@@ -249,7 +261,13 @@ void fill_common(GemmParams& p, const Scalars& sc, const void* C, void* D, unsig
     memset(&p, 0, sizeof(p));
     p.D = D;
     p.status = status;
-    p.wait_limit_ns = 4000000000ull;
+    // every wait inside the kernels gives up after this long (DECXB200_WAIT_LIMIT_MS, default 4 s)
+    static const unsigned long long limit_ns = [] {
+        const char* e = getenv("DECXB200_WAIT_LIMIT_MS");
+        const long v = e ? atol(e) : 0;
+        return v > 0 ? (unsigned long long)v * 1000000ull : 4000000000ull;
+    }();
+    p.wait_limit_ns = limit_ns;
     p.alpha_re = sc.ar;
     p.alpha_im = sc.ai;
     p.beta_re = sc.br;
@@ -258,9 +276,16 @@ void fill_common(GemmParams& p, const Scalars& sc, const void* C, void* D, unsig
     p.C = use_c ? C : nullptr;
 }
 
+struct PanelGate {            // B arrives in column panels while the kernel runs (see GemmParams)
+    uint32_t n = 0;
+    uint32_t col_end[MAX_PANELS] = {0};
+    const unsigned* flags = nullptr;
+    unsigned epoch = 0;
+};
+
 int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
             const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc,
-            unsigned* status, int cta_group, int max_ctas) {
+            unsigned* status, int cta_group, int max_ctas, const PanelGate* gate = nullptr) {
     if ((lda % 8) != 0 || (ldb % 8) != 0 || !aligned16(A) || !aligned16(B)) return DECXB200_EALIGN;
     GemmParams p;
     fill_common(p, sc, C, D, status);
@@ -269,6 +294,12 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
     p.epi_mode = EPI_REAL;
     p.vec_d = ((ldd % 8) == 0 && aligned16(D)) ? 1 : 0;
     p.vec_c = (p.C != nullptr && (ldc % 8) == 0 && aligned16(C)) ? 1 : 0;
+    if (gate != nullptr && gate->n > 0) {
+        p.n_panels = gate->n;
+        for (uint32_t i = 0; i < gate->n; ++i) p.panel_end[i] = gate->col_end[i];
+        p.panel_flags = gate->flags;
+        p.panel_epoch = gate->epoch;
+    }
     using C1 = GemmCfg<0, 1>;
     CUtensorMap a0, b0;
     int rc;
@@ -287,6 +318,9 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
         const double t_plain = double((plain + pairs - 1) / pairs);
         const double t_wide = double((wide + pairs - 1) / pairs) * 2.0 * 0.92;
         nacc = (K >= 2048 && t_wide < t_plain) ? 2 : 1;
+        if (gate != nullptr && gate->n > 1)                     // panel ends must be tile boundaries
+            for (uint32_t i = 0; i + 1 < gate->n; ++i)
+                if (gate->col_end[i] % 512 != 0) nacc = 1;
         if (nacc_env == 1 || nacc_env == 2) nacc = nacc_env;
     }
     // one 3-D load per stage when reading the last column chunk at full width stays inside B's rows
@@ -620,6 +654,53 @@ int decxb200_gemm_fp32_noalloc(void* stream_, uint32_t M, uint32_t N, uint32_t K
     if ((rc = prep_b(stream, false, B, ldb, K, N, b_hi, b_lo, ldbw)) != 0) return rc;
     return run_tf32(stream, dev, false, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, C, ldc, D, ldd, sc, status,
                     cta_group, 0);
+}
+
+int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
+                              const void* B, uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
+                              const uint32_t* panel_col_end, const unsigned* panel_flags, unsigned epoch,
+                              int max_ctas) {
+    t_launches = 0;
+    int dev = 0, cta_group = 2;
+    int rc = check_common(DECXB200_FP16, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, cta_group, dev);
+    if (rc != 0) return rc;
+    if (n_panels == 0 || n_panels > uint32_t(MAX_PANELS) || panel_col_end == nullptr || panel_flags == nullptr)
+        return DECXB200_EINVAL;
+    PanelGate g;
+    g.n = n_panels;
+    uint32_t prev = 0;
+    for (uint32_t i = 0; i < n_panels; ++i) {
+        if (panel_col_end[i] <= prev || panel_col_end[i] > N) return DECXB200_EINVAL;
+        g.col_end[i] = prev = panel_col_end[i];
+    }
+    if (prev != N) return DECXB200_EINVAL;
+    g.flags = panel_flags;
+    g.epoch = epoch;
+    return run_f16(reinterpret_cast<cudaStream_t>(stream_), dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(),
+                   status, 2, max_ctas, &g);
+}
+
+int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes,
+                          size_t rows) {
+    const cudaError_t e = cudaMemcpy2DAsync(dst, dpitch, src, spitch, width_bytes, rows, cudaMemcpyDefault,
+                                            reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+int decxb200_write_flag_async(void* stream, unsigned* flag, unsigned value) {
+    typedef CUresult (*WriteValueFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    static WriteValueFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<WriteValueFn>(p);
+    });
+    if (fn == nullptr || flag == nullptr) return DECXB200_EDRIVER;
+    const CUresult r = fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), value, 0);
+    return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
 int decxb200_ipc_alloc(size_t bytes, void** dptr) {

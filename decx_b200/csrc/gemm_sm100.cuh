@@ -56,7 +56,9 @@ enum KernelStatus : unsigned {
     KS_TIMEOUT_MMA_ACC = 0x103,
     KS_TIMEOUT_EPILOGUE = 0x104,
     KS_TIMEOUT_TAIL = 0x105,
+    KS_TIMEOUT_PANEL = 0x106,
 };
+constexpr int MAX_PANELS = 8;
 
 struct GemmParams {
     uint32_t M, N, K;          // real problem extents seen by the MMA (complex: N, K doubled)
@@ -74,6 +76,14 @@ struct GemmParams {
     uint32_t group_m;          // rasterisation group height, in tiles
     unsigned* status;          // device word, may be nullptr
     unsigned long long wait_limit_ns;
+    // Column panels of B that arrive while the kernel runs (row-sharded multi-GPU GEMM): tiles are walked panel
+    // by panel, and before a producer loads its first tile of panel i it waits (bounded) until
+    // panel_flags[i] has reached panel_epoch -- written, after the panel's data, by the stream that delivers B.
+    // n_panels == 1 and panel_flags == nullptr for an ordinary GEMM.
+    uint32_t n_panels;
+    uint32_t panel_end[MAX_PANELS];   // exclusive end of each panel, in tile columns
+    const unsigned* panel_flags;
+    unsigned panel_epoch;
     // soft lockstep of the persistent CTAs (see g_wave_ticket)
     unsigned sync_base;        // value of the ticket counter when this launch starts
     unsigned sync_on;          // 0 = off
@@ -122,14 +132,24 @@ struct GemmCfg {
 
 // tile index -> (tile_m, tile_n), walking groups of `group_m` tile rows column by column
 // so that the CTAs running at one time share a small set of A rows and B columns in L2.
-__device__ __forceinline__ void tile_coords(uint32_t t, const GemmParams& p, uint32_t& tm, uint32_t& tn) {
-    const uint32_t per_group = p.group_m * p.tiles_n;
+// Panels (see GemmParams) are the outermost level: all tiles of panel 0 come first.  Returns the panel index.
+__device__ __forceinline__ uint32_t tile_coords(uint32_t t, const GemmParams& p, uint32_t& tm, uint32_t& tn) {
+    uint32_t begin = 0, pi = 0;
+    for (;; ++pi) {
+        const uint32_t cnt = p.tiles_m * (p.panel_end[pi] - begin);
+        if (t < cnt || pi + 1 >= p.n_panels) break;
+        t -= cnt;
+        begin = p.panel_end[pi];
+    }
+    const uint32_t width = p.panel_end[pi] - begin;
+    const uint32_t per_group = p.group_m * width;
     const uint32_t g = t / per_group;
     const uint32_t first_m = g * p.group_m;
     const uint32_t rows = min(p.group_m, p.tiles_m - first_m);
     const uint32_t r = t - g * per_group;
     tm = first_m + r % rows;
-    tn = r / rows;
+    tn = begin + r / rows;
+    return pi;
 }
 
 __device__ __forceinline__ void report(const GemmParams& p, unsigned code) {
@@ -321,7 +341,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             tma_prefetch_desc(&tmB0);
             if constexpr (KIND == 1) { tma_prefetch_desc(&tmA1); tma_prefetch_desc(&tmB1); }
             const uint32_t full_target = (CTAS == 2) ? map_to_cta(full_bar, 0) : full_bar;
-            uint32_t s = 0, ph = 0, my_iter = 0;
+            uint32_t s = 0, ph = 0, my_iter = 0, cur_panel = 0xFFFFFFFFu;
             bool ok = true;
             for (uint32_t t = worker; t < n_tiles && ok; t += n_workers, ++my_iter) {
                 if (p.sync_on && leader && my_iter > 0) {
@@ -334,7 +354,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     }
                 }
                 uint32_t tm, tn;
-                tile_coords(t, p, tm, tn);
+                const uint32_t panel = tile_coords(t, p, tm, tn);
+                if (p.panel_flags != nullptr && panel != cur_panel) {
+                    // B's panel may still be on its way: wait for its arrival flag, then make the data it
+                    // guards visible to the TMA loads
+                    const uint64_t t0 = global_timer_ns();
+                    bool arrived = true;
+                    while (int(ld_acquire_sys(p.panel_flags + panel) - p.panel_epoch) < 0) {
+                        if (global_timer_ns() - t0 > limit) { arrived = false; break; }
+                    }
+                    if (!arrived) {
+                        report(p, KS_TIMEOUT_PANEL);
+                        ok = false;
+                        break;
+                    }
+                    fence_proxy_async_all();
+                    cur_panel = panel;
+                }
                 const int32_t row0 = int32_t((tm * CTAS + cta_rank) * Cfg::BM);
                 const int32_t col0 = int32_t(tn * Cfg::BN_TILE + cta_rank * Cfg::BN_LOAD);
                 for (uint32_t kb = 0; kb < n_kb; ++kb) {

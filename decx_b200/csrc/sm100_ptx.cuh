@@ -41,6 +41,15 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
     return r;
 }
 
+// word written by a copy engine / stream memory operation, possibly on behalf of another GPU
+__device__ __forceinline__ uint32_t ld_acquire_sys(const unsigned* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// order earlier generic-proxy observations before later async-proxy (TMA) accesses, all state spaces
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------

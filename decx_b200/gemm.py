@@ -117,3 +117,31 @@ def gemm_raw(dt, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd, alpha=
     capi.check(capi.lib.decxb200_gemm_ex(dt, stream, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd,
                                          pa, pb, ws_ptr, ws_bytes, status_ptr, cta_group, max_ctas))
     return capi.lib.decxb200_last_launch_count()
+
+
+def gemm_fp16_panels(A, B, out, panel_col_end, flags, epoch, status=None, max_ctas=0):
+    """One GEMM launch over a B that arrives panel by panel (``decxb200_gemm_fp16_panels``).
+
+    ``flags`` is an int32/uint32 CUDA tensor with one word per panel; the stream that fills panel i writes
+    ``epoch`` there afterwards (``write_flag``).  Launches on torch's current stream; returns ``out``."""
+    M, K = A.shape
+    N = B.shape[1]
+    ends = (ctypes.c_uint32 * len(panel_col_end))(*panel_col_end)
+    with torch.cuda.device(A.device):
+        code = capi.lib.decxb200_gemm_fp16_panels(
+            torch.cuda.current_stream().cuda_stream, M, N, K, A.data_ptr(), _ld(A), B.data_ptr(), _ld(B),
+            out.data_ptr(), _ld(out), status.data_ptr() if status is not None else None,
+            len(panel_col_end), ends, flags.data_ptr(), epoch, max_ctas)
+    capi.check(code)
+    return out
+
+
+def write_flag(flags, index, value, stream=None):
+    """Stream-ordered store of ``value`` to ``flags[index]`` without a kernel (cuStreamWriteValue32)."""
+    s = (stream or torch.cuda.current_stream(flags.device)).cuda_stream
+    capi.check(capi.lib.decxb200_write_flag_async(s, flags.data_ptr() + 4 * index, value))
+
+
+def copy2d(dst_ptr, dpitch, src_ptr, spitch, width_bytes, rows, stream):
+    """Copy-engine 2-D copy between raw device addresses (peer mappings allowed)."""
+    capi.check(capi.lib.decxb200_copy2d_async(stream.cuda_stream, dst_ptr, dpitch, src_ptr, spitch, width_bytes, rows))

@@ -151,6 +151,28 @@ DECXB200_API int decxb200_gemm_fp32_noalloc(void* stream, uint32_t M, uint32_t N
  * have no counterpart there.
  */
 DECXB200_API int decxb200_ipc_alloc(size_t bytes, void** dptr);
+
+/*
+ * fp16 GEMM whose B operand is still arriving (row-sharded multi-GPU GEMM; no counterpart in the
+ * single-GPU reference).  B is a full K x N row-major replica in this GPU's memory that another
+ * stream fills column panel by column panel (panel i = columns [panel_col_end[i-1], panel_col_end[i]),
+ * at most 8 panels, the last end = N, the others multiples of 256).  After panel i's data, that stream
+ * writes `epoch` to panel_flags[i] (decxb200_write_flag_async).  ONE kernel launch computes D = A.B: it
+ * walks the tiles panel by panel and its loader waits -- bounded, then status word 0x106 -- for a panel's
+ * flag before it touches that panel, so the transfer of B overlaps the tiles of the panels before it.
+ * Epochs must increase from one use of the flags to the next.
+ */
+DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N, uint32_t K,
+                                           const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                                           void* D, uint64_t ldd, unsigned* status,
+                                           uint32_t n_panels, const uint32_t* panel_col_end,
+                                           const unsigned* panel_flags, unsigned epoch, int max_ctas);
+/* 2-D copy by the copy engines between any two device buffers this process can address (peer mappings
+ * included): `rows` rows of `width_bytes`, rows dpitch / spitch bytes apart.  cudaMemcpy2DAsync. */
+DECXB200_API int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch,
+                                       size_t width_bytes, size_t rows);
+/* Stream-ordered 32-bit store (cuStreamWriteValue32): no kernel, so it cannot be starved of an SM. */
+DECXB200_API int decxb200_write_flag_async(void* stream, unsigned* flag, unsigned value);
 DECXB200_API int decxb200_ipc_free(void* dptr);
 DECXB200_API int decxb200_ipc_export(void* dptr, unsigned char handle[64]);
 DECXB200_API int decxb200_ipc_open(const unsigned char handle[64], void** peer_ptr);
