@@ -220,6 +220,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--panels", default="ramp", help="column panels of B in the sharded path: a count or 'ramp'")
     ap.add_argument("--bcast", default=None, choices=[None, "p2p", "broadcast", "scatter_allgather"])
+    ap.add_argument("--overlap", default=None, choices=[None, "single", "panels"])
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--kernel-only", action="store_true",
@@ -284,7 +285,7 @@ def main():
 
     # ------------------------------------------------------------ device-resident measurement
     panels = args.panels if args.panels == "ramp" else int(args.panels)
-    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast)
+    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast, overlap=args.overlap)
     if sg.nrows:
         sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
     if sg.is_owner:
@@ -319,21 +320,20 @@ def main():
 
     # dominant kernel alone (no communication): CUDA events around this rank's GEMM launches
     kern_ms = []
+    n_launch = 1
     if sg.nrows:
         for _ in range(2):
-            for j in range(len(sg.panels)):
-                sg._panel_gemm(j)
+            n_launch = sg.compute_only()
         torch.cuda.synchronize(device)
         for _ in range(3):
-            for j in range(len(sg.panels)):
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                sg._panel_gemm(j)
-                e1.record()
-                torch.cuda.synchronize(device)
-                kern_ms.append(e0.elapsed_time(e1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            n_launch = sg.compute_only()
+            e1.record()
+            torch.cuda.synchronize(device)
+            kern_ms.append(e0.elapsed_time(e1) / max(n_launch, 1))
     barrier()
-    flops_per_launch = flops / world / len(sg.panels)
+    flops_per_launch = flops / world / max(n_launch, 1)
     kern_avg = max_over_ranks(sum(kern_ms) / len(kern_ms) if kern_ms else 0.0)
     achieved = flops_per_launch / (kern_avg * 1e-3) / 1e12 if kern_avg else 0.0
     peak = tensor_peak(dtype, pk)
@@ -400,7 +400,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": ARITH[dtype], "data": "synthetic (seeded, generated on the device)",
         "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
-                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, gather={sg.gather}" if world > 1 else ""),
+                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, overlap={sg.overlap}, gather={sg.gather}" if world > 1 else ""),
                    "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30)},
         "pct_of_peak": {"value": 100 * value / (world * peak), "denominator_tflops": world * peak,
                         "which": f"{pk['source']} bf16 burst x {world} GPU(s)" + ("" if dtype == "float16" else ", /2 for TF32, /3 for 3xTF32"),

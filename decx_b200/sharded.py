@@ -24,6 +24,13 @@ layer is new surface on top of the same per-GPU GEMM.  One step is:
      form the CPU tests run over gloo with an injected host GEMM);
   4. a barrier across the ranks closes the step.
 
+fp16 on GPUs runs steps 1 and 2 as ONE kernel launch per rank ("single" overlap): every rank keeps a full
+row-major replica of B in symmetric memory, the copy engines fill it panel by panel (same pull pattern as
+"p2p", 2-D copies) and write a flag per panel with a stream memory operation; the GEMM is launched at once,
+walks its tiles panel by panel and its loader waits on a panel's flag before touching it
+(decxb200_gemm_fp16_panels).  No per-panel launches, so no round of the persistent grid is left half empty
+at a panel boundary, and the 256 x 512 tile applies.
+
 Rows are dealt in multiples of 256 (the CTA-pair tile height), so every rank runs whole tiles.
 """
 import ctypes
@@ -105,7 +112,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None):
+                 reserve_sms=None, bcast=None, overlap=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -128,12 +135,21 @@ class ShardedGemm:
         dev = self.device
         self.A = torch.empty((max(self.nrows, 1), K), dtype=dtype, device=dev)[: self.nrows]
         self.B = torch.empty((K, N), dtype=dtype, device=dev) if self.is_owner else None
+        self._epoch = 0
         self._hdl = None
+        self.overlap = "panels"                 # one GEMM launch per panel
         if self.world > 1 and self.bcast == "p2p" and (not self.on_gpu or K % self.world != 0):
             self.bcast = "broadcast"
-        if self.world > 1 and self.bcast == "p2p":
+        if (overlap in (None, "single") and self.world > 1 and self.bcast == "p2p" and dtype == torch.float16
+                and gemm_fn is None and self.gather == "peer" and N % 8 == 0):
+            self.panels = panel_plan(N, panels, align=512)
+            if len(self.panels) <= 8 and self._setup_symmetric_replica():
+                self.overlap = "single"
+        if self.world > 1 and self.bcast == "p2p" and self.overlap != "single":
             self._setup_symmetric_panels()
-        if self.world > 1 and self._hdl is None:
+        if self.overlap == "single":
+            self.Bp = None
+        elif self.world > 1 and self._hdl is None:
             self.Bp = [torch.empty((K, w), dtype=dtype, device=dev) for _, w in self.panels]
         elif self.world == 1:
             self.Bp = [self.B]
@@ -186,6 +202,71 @@ class ShardedGemm:
                   file=sys.stderr)
             self._hdl = None
             self.bcast = "broadcast"
+
+    def _setup_symmetric_replica(self):
+        """"single" overlap: a full K x N replica of B per rank in symmetric memory (the owner's is B itself)."""
+        import sys
+        try:
+            import torch.distributed._symmetric_memory as symm
+            self._bsym = symm.empty(self.K * self.N, dtype=self.dtype, device=self.device)
+            grp = self.group if self.group is not None else dist.group.WORLD
+            self._hdl = symm.rendezvous(self._bsym, group=grp)
+            self._bptrs = [int(p) for p in self._hdl.buffer_ptrs]
+            self.Bfull = self._bsym.view(self.K, self.N)
+            if self.is_owner:
+                self.B = self.Bfull               # the owner's operand IS its replica: nothing to pack
+            self.flags = torch.zeros(8, dtype=torch.int32, device=self.device)
+            return True
+        except Exception as e:
+            print(f"decx_b200.sharded: symmetric memory unavailable ({type(e).__name__}: {e}); one launch per panel",
+                  file=sys.stderr)
+            self._hdl = None
+            self.bcast = "broadcast"
+            return False
+
+    def _deliver_replica(self, epoch):
+        """Communication stream of the "single" overlap: fill this rank's replica of B panel by panel and flag
+        each panel.  Every rank pulls its row block of the panel from the owner, then the other row blocks from
+        the ranks that hold them; copy engines only, ordered by symmetric-memory stream barriers."""
+        G, st = self._G, self.comm_stream
+        esz, N, rows = self._esz, self.N, self.K // self.world
+        pitch = N * esz
+        self._hdl.barrier(channel=0)                       # the owner's B is final; nobody still reads old data
+        for j, (c0, w) in enumerate(self.panels):
+            if self.is_owner:
+                G.write_flag(self.flags, j, epoch, st)     # the owner holds every panel already
+                self._hdl.barrier(channel=1)
+                continue
+            mine = (self.rank * rows * N + c0) * esz
+            G.copy2d(self._bptrs[self.rank] + mine, pitch, self._bptrs[self.owner] + mine, pitch, w * esz, rows, st)
+            self._hdl.barrier(channel=1)                   # every rank holds its own row block of panel j
+            for d in range(1, self.world):
+                src = (self.rank + d) % self.world
+                off = (src * rows * N + c0) * esz
+                G.copy2d(self._bptrs[self.rank] + off, pitch, self._bptrs[src] + off, pitch, w * esz, rows, st)
+            G.write_flag(self.flags, j, epoch, st)
+
+    def _single_gemm(self, epoch):
+        if self.nrows == 0:
+            return
+        ends = [c0 + w for c0, w in self.panels]
+        arr = (ctypes.c_uint32 * len(ends))(*ends)
+        capi = self._capi
+        capi.check(capi.lib.decxb200_gemm_fp16_panels(
+            torch.cuda.current_stream(self.device).cuda_stream, self.nrows, self.N, self.K,
+            self.A.data_ptr(), self.A.stride(0), self.Bfull.data_ptr(), self.N, self._d_ptr, self.N,
+            self.status.data_ptr(), len(ends), arr, self.flags.data_ptr(), epoch, self._max_ctas))
+        self.launches += capi.lib.decxb200_last_launch_count()
+
+    def compute_only(self):
+        """This rank's GEMM launch(es) with B already in place and no communication (for kernel timing)."""
+        self.launches = 0
+        if self.overlap == "single":
+            self._single_gemm(self._epoch)                 # the flags already hold this epoch
+        else:
+            for j in range(len(self.panels)):
+                self._panel_gemm(j)
+        return self.launches
 
     def _send_panel_p2p(self, j):
         c0, w = self.panels[j]
@@ -291,6 +372,17 @@ class ShardedGemm:
         if self.world == 1:
             self.Bp = [self.B]
             self._panel_gemm(0)
+            return
+        if self.overlap == "single":
+            with torch.cuda.device(self.device):
+                cur = torch.cuda.current_stream(self.device)
+                self._epoch += 1
+                self.comm_stream.wait_stream(cur)          # the previous step no longer reads the replica
+                with torch.cuda.stream(self.comm_stream):
+                    self._deliver_replica(self._epoch)
+                self._single_gemm(self._epoch)             # waits on the panel flags inside the kernel
+                dist.barrier(group=self.group)             # every rank's rows have reached the owner
+                cur.wait_stream(self.comm_stream)
             return
         if self.on_gpu:
             with torch.cuda.device(self.device):
