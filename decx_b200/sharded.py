@@ -216,6 +216,9 @@ class ShardedGemm:
             if self.is_owner:
                 self.B = self.Bfull               # the owner's operand IS its replica: nothing to pack
             self.flags = torch.zeros(8, dtype=torch.int32, device=self.device)
+            self._side = [torch.cuda.Stream(device=self.device) for _ in range(2)]
+            self._ev_go = torch.cuda.Event()
+            self._ev_side = [torch.cuda.Event() for _ in self._side]
             return True
         except Exception as e:
             print(f"decx_b200.sharded: symmetric memory unavailable ({type(e).__name__}: {e}); one launch per panel",
@@ -240,10 +243,25 @@ class ShardedGemm:
             mine = (self.rank * rows * N + c0) * esz
             G.copy2d(self._bptrs[self.rank] + mine, pitch, self._bptrs[self.owner] + mine, pitch, w * esz, rows, st)
             self._hdl.barrier(channel=1)                   # every rank holds its own row block of panel j
+            # the other row blocks, each in two halves, dealt over several streams: one stream's copies run one
+            # after the other on one copy engine, and a single engine pulling from peers is far below link speed
+            self._ev_go.record(st)
+            for side in self._side:
+                side.wait_event(self._ev_go)
+            lanes, k = [st] + self._side, 0
+            half = rows // 2
             for d in range(1, self.world):
                 src = (self.rank + d) % self.world
-                off = (src * rows * N + c0) * esz
-                G.copy2d(self._bptrs[self.rank] + off, pitch, self._bptrs[src] + off, pitch, w * esz, rows, st)
+                for r0, nr in ((0, half), (half, rows - half)):
+                    if nr == 0:
+                        continue
+                    off = ((src * rows + r0) * N + c0) * esz
+                    k += 1
+                    G.copy2d(self._bptrs[self.rank] + off, pitch, self._bptrs[src] + off, pitch, w * esz, nr,
+                             lanes[k % len(lanes)])
+            for side, ev in zip(self._side, self._ev_side):
+                ev.record(side)
+                st.wait_event(ev)
             G.write_flag(self.flags, j, epoch, st)
 
     def _single_gemm(self, epoch):
