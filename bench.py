@@ -407,7 +407,7 @@ def main():
                         "of_sustained": (100 * value / (world * pk["bf16_sustained"] / (1 if dtype == "float16" else 6))) if pk["bf16_sustained"] else None},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, world)),
-                     "kernel": "gemm_tcgen05_kernel<%d,2>" % (0 if dtype == "float16" else 1),
+                     "kernel": "gemm_tcgen05_kernel<0,2,2>" if dtype == "float16" else "gemm_tcgen05_kernel<1,2,1>",
                      "launch_ms": kern_avg, "flops_per_launch": flops_per_launch,
                      "peak_source": f"{pk['source']}: bf16 burst {pk['bf16']} TFLOP/s" + ("" if dtype == "float16" else " /6 (TF32 rate, three MMAs per product)")},
         "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -437,9 +437,9 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu
 # captures summarised under profiles/ (None = not captured for that configuration)
-# fp16 16384^3: 8.84 GB read + 0.54 GB written (profiles/gemm_tcgen05_f16_16384x16384x16384.md); config 5 has
+# fp16 16384^3: 6.71 GB read + 0.53 GB written (profiles/gemm_tcgen05_f16_16384x16384x16384.md); config 5 has
 # 4x the row slabs at the same N and K, so 4x the traffic per launch; fp32 8192^3 from its own capture.
-TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 9.38e9, ("cfg5", 1): 37.5e9, ("cfg2", 1): 4.83e9}
+TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 7.24e9, ("cfg5", 1): 29.0e9, ("cfg2", 1): 4.83e9}
 
 if __name__ == "__main__":
     main()

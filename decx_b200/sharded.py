@@ -58,17 +58,18 @@ def row_ranges(M, world, align=ROW_ALIGN):
 def panel_plan(N, panels, align=COL_ALIGN):
     """[(first_col, cols)] of the column panels of B.
 
-    `panels` is a count (near-equal multiples of `align`), a list of widths, or "ramp": a small first panel
-    (N/16) so that the first GEMM can start early, then 3N/16, then quarters -- nothing hides the arrival of
-    the first panel, everything after it travels while a GEMM runs."""
+    `panels` is a count (near-equal multiples of `align`), a list of widths, or "ramp": small first and last
+    panels (N/16 each) around three large ones.  The step ends at
+        max( arrival of the first panel + all the compute ,  end of the delivery + compute of the last panel )
+    -- the first term rules when the GEMM is slower than the delivery, the second when it is faster -- so
+    both the first and the last panel should be small."""
     if panels == "ramp":
         units = (N + align - 1) // align
         if units < 16:
             return panel_plan(N, min(4, units), align)
-        first, second = max(1, units // 16), max(1, 3 * units // 16)
-        rest = units - first - second
-        q, extra = divmod(rest, 3)
-        widths = [first, second] + [q + (1 if i < extra else 0) for i in range(3)]
+        edge = max(1, units // 16)
+        q, extra = divmod(units - 2 * edge, 3)
+        widths = [edge] + [q + (1 if i < extra else 0) for i in range(3)] + [edge]
         panels = [w * align for w in widths if w > 0]
     if isinstance(panels, (list, tuple)):
         out, c = [], 0
