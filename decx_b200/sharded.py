@@ -58,18 +58,17 @@ def row_ranges(M, world, align=ROW_ALIGN):
 def panel_plan(N, panels, align=COL_ALIGN):
     """[(first_col, cols)] of the column panels of B.
 
-    `panels` is a count (near-equal multiples of `align`), a list of widths, or "ramp": small first and last
-    panels (N/16 each) around three large ones.  The step ends at
-        max( arrival of the first panel + all the compute ,  end of the delivery + compute of the last panel )
-    -- the first term rules when the GEMM is slower than the delivery, the second when it is faster -- so
-    both the first and the last panel should be small."""
+    `panels` is a count (near-equal multiples of `align`), a list of widths, or "ramp": a small first panel
+    (N/16) so that the first tiles can start early, then 3N/16, then quarters -- nothing hides the arrival of
+    the first panel, everything after it travels while tiles are being computed.  (Measured at 8 GPUs on
+    65536 x 16384 x 16384: ramp 4.08-4.17 ms per step; small first AND last panel 4.30 ms.)"""
     if panels == "ramp":
         units = (N + align - 1) // align
         if units < 16:
             return panel_plan(N, min(4, units), align)
-        edge = max(1, units // 16)
-        q, extra = divmod(units - 2 * edge, 3)
-        widths = [edge] + [q + (1 if i < extra else 0) for i in range(3)] + [edge]
+        first, second = max(1, units // 16), max(1, 3 * units // 16)
+        q, extra = divmod(units - first - second, 3)
+        widths = [first, second] + [q + (1 if i < extra else 0) for i in range(3)]
         panels = [w * align for w in widths if w > 0]
     if isinstance(panels, (list, tuple)):
         out, c = [], 0

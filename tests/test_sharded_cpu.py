@@ -34,8 +34,8 @@ def test_panel_plan():
     assert panel_plan(16384, 4) == [(0, 4096), (4096, 4096), (8192, 4096), (12288, 4096)]
     assert panel_plan(3001, 4) == [(0, 768), (768, 768), (1536, 768), (2304, 697)]
     assert panel_plan(100, 8) == [(0, 100)]
-    assert [w for _, w in panel_plan(16384, "ramp")] == [1024, 4864, 4864, 4608, 1024]
-    assert [w for _, w in panel_plan(16384, "ramp", align=512)] == [1024, 5120, 4608, 4608, 1024]
+    assert [w for _, w in panel_plan(16384, "ramp")] == [1024, 3072, 4096, 4096, 4096]
+    assert [w for _, w in panel_plan(16384, "ramp", align=512)] == [1024, 3072, 4096, 4096, 4096]
     assert panel_plan(3001, "ramp") == panel_plan(3001, 4)          # too narrow to ramp
     assert panel_plan(1000, [256, 512]) == [(0, 256), (256, 512), (768, 232)]
     for N in (1, 255, 257, 3001, 16384):
