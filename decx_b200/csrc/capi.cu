@@ -36,7 +36,6 @@ struct DeviceInfo {
     unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
     bool attr_set[2][2][2] = {};
-    int max_pairs[2] = {0, 0};
 };
 DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;

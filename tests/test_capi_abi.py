@@ -58,3 +58,24 @@ def test_bad_arguments_are_rejected_without_a_gpu():
     assert g(*args(capi.FP32, 4, 4, 4, None, p, p)) == -1  # null operand
     assert g(*args(capi.FP32, 4, 4, 4, p, p, p, lda=3)) == -1  # pitch smaller than width
     assert capi.lib.decxb200_gemm_ex(*args(capi.FP32, 4, 4, 4, p, p, p), 3, 0) == -1  # bad cta_group
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/decx_b200.h is a C header: it must compile as C99 on its own."""
+    import subprocess
+    src = tmp_path / "use.c"
+    src.write_text('#include "decx_b200.h"\nint main(void) { return decxb200_gemm_workspace_bytes(DECXB200_FP16, 1, 1, 1) != 0; }\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), "-c", str(src),
+                    "-o", str(tmp_path / "use.o")], check=True)
+
+
+def test_front_end_refuses_host_tensors_and_missing_gpu():
+    """No fallback: the device front end rejects CPU tensors instead of computing on the host."""
+    import pytest
+    import torch
+    from decx_b200 import gemm as G
+    with pytest.raises(RuntimeError):
+        G.gemm(torch.zeros(4, 4), torch.zeros(4, 4))
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            G.gemm_host(torch.zeros(4, 4), torch.zeros(4, 4))

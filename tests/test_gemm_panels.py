@@ -44,7 +44,7 @@ def test_kernel_waits_for_panels_delivered_by_another_stream():
     out = torch.empty((2048, 4096), dtype=torch.float16, device=dev)
     torch.cuda.synchronize()
     side = torch.cuda.Stream(dev)
-    G.gemm_fp16_panels(A, B if False else Bdst, out, ends, flags, 1, status=st)     # spins until panel 0 arrives
+    G.gemm_fp16_panels(A, Bdst, out, ends, flags, 1, status=st)     # its loader waits until panel 0 arrives
     time.sleep(0.05)
     lo = 0
     with torch.cuda.stream(side):
