@@ -67,8 +67,10 @@ _DECX_API_ const cudaDeviceProp& _get_cuda_prop();
 }  // namespace cuda
 
 // ------------------------------------------------------------------------------------------------ device pool
+class MemPool_D;
 // One block of a pooled chunk (reference: srcs/modules/core/memory_management/MemBlock.h:46-96).
 struct MemBlock {
+    MemPool_D* pool = nullptr;  // the pool (= device) the block belongs to: it is always returned there
     uint8_t* ptr = nullptr;
     uint64_t size = 0;          // bytes, a multiple of 256
     bool idle = true;

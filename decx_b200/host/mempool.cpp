@@ -59,6 +59,7 @@ int decx::MemPool_D::allocate(uint64_t bytes, decx::MemBlock** out) {
         const int rc = g_raw_alloc(&base, size_t(csize));
         if (rc != 0 || base == nullptr) return rc != 0 ? rc : int(cudaErrorMemoryAllocation);
         decx::MemBlock* b = new decx::MemBlock;
+        b->pool = this;
         b->ptr = static_cast<uint8_t*>(base);
         b->size = csize;
         b->chunk = int(_chunks.size());
@@ -67,6 +68,7 @@ int decx::MemPool_D::allocate(uint64_t bytes, decx::MemBlock** out) {
     }
     if (hit->size > need) {   // split: [need | remainder]
         decx::MemBlock* rest = new decx::MemBlock;
+        rest->pool = this;
         rest->ptr = hit->ptr + need;
         rest->size = hit->size - need;
         rest->chunk = hit->chunk;
@@ -209,15 +211,11 @@ int decx::alloc::_device_realloc(decx::PtrInfo<void>* p, uint64_t bytes, bool se
 }
 
 void decx::alloc::_device_dealloc(decx::PtrInfo<void>* p) {
-    if (p->block != nullptr) {
-        // the block knows its chunk, not its pool: pools are per device and a block is returned on the
-        // device it came from, which callers keep current (the containers remember their ordinal)
-        decx::MemPool_D::GetInstance(current_device())->deallocate(p->block);
-    }
+    if (p->block != nullptr) p->block->pool->deallocate(p->block);   // back to the pool (device) it came from
     p->block = nullptr;
     p->ptr = nullptr;
 }
 
 void decx::alloc::_device_malloc_same_place(decx::PtrInfo<void>* p) {
-    if (p->block != nullptr) decx::MemPool_D::GetInstance(current_device())->register_reference(p->block);
+    if (p->block != nullptr) p->block->pool->register_reference(p->block);
 }

@@ -99,6 +99,7 @@ static void test_pool() {
     decx::MemPool_D* pool = decx::MemPool_D::GetInstance(63);       // an ordinal nothing else uses
     decx::MemBlock *a, *b, *c, *d;
     CHECK(pool->allocate(1000, &a) == 0 && a->size == 1024);        // rounded to 256
+    CHECK(a->pool == pool);                                         // a block remembers where it goes back to
     CHECK(pool->chunk_count() == 1 && pool->bytes_reserved() == (1u << 20) && g_allocs == 1);
     CHECK(pool->allocate(300000, &b) == 0 && pool->allocate(5, &c) == 0);
     CHECK(g_allocs == 1);                                           // carved from the same chunk
