@@ -61,7 +61,7 @@ decx::ScratchResource* arena_cache() {
 
 // one status word per device for the kernels' bounded waits, and a pinned host copy to read it back
 struct StatusWord {
-    decx::PtrInfo<void> dev;
+    struct { void* ptr = nullptr; } dev;   // 4 bytes straight from cudaMalloc: must outlive a release of the pool
     unsigned* host = nullptr;
 };
 StatusWord* status_word(int device) {
@@ -71,10 +71,15 @@ StatusWord* status_word(int device) {
     if (device < 0 || device >= 64) return nullptr;
     StatusWord& w = words[device];
     if (w.dev.ptr == nullptr) {
-        if (decx::alloc::_device_malloc(&w.dev, sizeof(unsigned), true, nullptr) != 0) return nullptr;
+        if (cudaMalloc(&w.dev.ptr, sizeof(unsigned)) != cudaSuccess || cudaMemset(w.dev.ptr, 0, sizeof(unsigned)) != cudaSuccess) {
+            cudaGetLastError();
+            w.dev.ptr = nullptr;
+            return nullptr;
+        }
         if (cudaHostAlloc(reinterpret_cast<void**>(&w.host), sizeof(unsigned), cudaHostAllocDefault) != cudaSuccess) {
             cudaGetLastError();
-            decx::alloc::_device_dealloc(&w.dev);
+            cudaFree(w.dev.ptr);
+            w.dev.ptr = nullptr;
             return nullptr;
         }
         *w.host = 0;
