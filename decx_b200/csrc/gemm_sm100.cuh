@@ -10,7 +10,14 @@
 //               B (consumed MN-major, so B is never transposed) into a ring of stages
 //   warp 1      allocates TMEM and issues tcgen05.mma; fp32 accumulators live in TMEM,
 //               two of them, so draining one overlaps the MMAs into the other
-//   warps 2..   epilogue: tcgen05.ld -> alpha/beta/C -> global stores (predicated edges)
+//   warps 2..   epilogue: tcgen05.ld -> alpha/beta/C -> a 32-row x 128-byte staging tile per warp in
+//               shared memory -> TMA bulk store (rows past M dropped by the hardware); predicated
+//               per-thread stores where D's rows are not 16-byte aligned or an N edge is ragged
+//
+// The CTAs are persistent (one per SM) and walk a rasterised tile list; a soft, time-limited barrier
+// between tile rounds keeps them at the same K position so that shared A/B slabs hit in L2
+// (g_wave_ticket).  Optionally B arrives while the kernel runs, in column panels guarded by flags
+// (GemmParams::panel_flags): the tile list is then ordered panel by panel.
 //
 // Accumulation chains.  The tensor core adds into its fp32 accumulator with truncation, so a
 // long chain of same-signed terms drifts by about (chain length) * 2^-24 relative -- 4e-6 at
@@ -38,7 +45,7 @@
 //         (eight warps, four per accumulator) no longer overlaps the next tile's MMAs: used for long K.
 //
 // Ragged M/N/K: tensor maps carry the logical extents, so out-of-range parts of a box
-// are zero-filled by TMA; stores are predicated.  No host-side padding.
+// are zero-filled by TMA on loads and dropped on stores.  No host-side padding.
 // Every wait is bounded: on time-out the role writes a code to *status and unwinds.
 #pragma once
 #include <cuda_fp16.h>
