@@ -41,7 +41,7 @@ def _load():
     lib.decxb200_gemm_fp32_noalloc.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp]
     lib.decxb200_gemm_fp16_panels.restype = ci
     lib.decxb200_gemm_fp16_panels.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32,
-                                              ctypes.POINTER(u32), vp, ctypes.c_uint, ci]
+                                              ctypes.POINTER(u32), vp, ctypes.c_uint, ci, ci]
     lib.decxb200_copy2d_async.restype = ci
     lib.decxb200_copy2d_async.argtypes = [vp, vp, sz, vp, sz, sz, sz]
     lib.decxb200_write_flag_async.restype = ci
@@ -59,6 +59,8 @@ def _load():
     lib.decxb200_ipc_close.argtypes = [vp]
     lib.decxb200_last_launch_count.restype = ci
     lib.decxb200_last_launch_count.argtypes = []
+    lib.decxb200_last_kernel_variant.restype = ci
+    lib.decxb200_last_kernel_variant.argtypes = []
     lib.decxb200_strerror.restype = ctypes.c_char_p
     lib.decxb200_strerror.argtypes = [ci]
     lib.decxb200_version.restype = ctypes.c_char_p
@@ -74,7 +76,7 @@ EXPORTS = [
     "decxb200_gemm_fp32_noalloc",
     "decxb200_gemm_fp16_panels", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
-    "decxb200_last_launch_count", "decxb200_strerror", "decxb200_version",
+    "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_strerror", "decxb200_version",
 ]
 
 

@@ -41,6 +41,7 @@ DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
 
 thread_local int t_launches = 0;
+thread_local int t_variant = 0;    // KIND*100 + CTAS*10 + NACC of the last GEMM kernel this thread launched
 
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
@@ -165,6 +166,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, p);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
+    t_variant = KIND * 100 + CTAS * 10 + NACC;
     return 0;
 }
 
@@ -306,6 +308,8 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
     // Two accumulators per tile (256 x 512 per CTA pair) when K is long enough to hide the unoverlapped epilogue
     // and there are at least two rounds of such tiles; DECXB200_NACC=1|2 overrides.
     int nacc = 1;
+    const bool force_wide = (cta_group == DECXB200_TILE_256x512);
+    if (force_wide) cta_group = 2;
     if (cta_group == 2) {
         static const int nacc_env = [] { const char* e = getenv("DECXB200_NACC"); return e ? atoi(e) : 0; }();
         int sms = 0;
@@ -321,6 +325,12 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
             for (uint32_t i = 0; i + 1 < gate->n; ++i)
                 if (gate->col_end[i] % 512 != 0) nacc = 1;
         if (nacc_env == 1 || nacc_env == 2) nacc = nacc_env;
+        if (force_wide) {
+            nacc = 2;
+            if (gate != nullptr && gate->n > 1)
+                for (uint32_t i = 0; i + 1 < gate->n; ++i)
+                    if (gate->col_end[i] % 512 != 0) return DECXB200_EINVAL;
+        }
     }
     // one 3-D load per stage when reading the last column chunk at full width stays inside B's rows
     p.b_chunked_map = ((N % C1::CHUNK_N) == 0 || ldb >= round_up(N, C1::CHUNK_N)) ? 1 : 0;
@@ -380,7 +390,8 @@ int check_common(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, u
     if (M == 0 || N == 0 || K == 0) return DECXB200_EINVAL;
     if (lda < K || ldb < N || ldd < N || (C != nullptr && ldc < N)) return DECXB200_EINVAL;
     if (cta_group == 0) cta_group = default_cta_group();
-    if (cta_group != 1 && cta_group != 2) return DECXB200_EINVAL;
+    if (cta_group != 1 && cta_group != 2 && !(cta_group == DECXB200_TILE_256x512 && dtype == DECXB200_FP16))
+        return DECXB200_EINVAL;
     if (dtype == DECXB200_CPLXF && (uint64_t(N) * 2 > 0xFFFFFFFFull || uint64_t(K) * 2 > 0xFFFFFFFFull))
         return DECXB200_ETOOLARGE;
     const cudaError_t ce = cudaGetDevice(&dev);
@@ -658,9 +669,9 @@ int decxb200_gemm_fp32_noalloc(void* stream_, uint32_t M, uint32_t N, uint32_t K
 int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
                               const void* B, uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
                               const uint32_t* panel_col_end, const unsigned* panel_flags, unsigned epoch,
-                              int max_ctas) {
+                              int max_ctas, int tile) {
     t_launches = 0;
-    int dev = 0, cta_group = 2;
+    int dev = 0, cta_group = (tile == DECXB200_TILE_256x512) ? tile : 2;
     int rc = check_common(DECXB200_FP16, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, cta_group, dev);
     if (rc != 0) return rc;
     if (n_panels == 0 || n_panels > uint32_t(MAX_PANELS) || panel_col_end == nullptr || panel_flags == nullptr)
@@ -676,7 +687,7 @@ int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K,
     g.flags = panel_flags;
     g.epoch = epoch;
     return run_f16(reinterpret_cast<cudaStream_t>(stream_), dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(),
-                   status, 2, max_ctas, &g);
+                   status, cta_group, max_ctas, &g);
 }
 
 int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes,
@@ -737,6 +748,7 @@ int decxb200_ipc_close(void* peer_ptr) {
 }
 
 int decxb200_last_launch_count(void) { return t_launches; }
+int decxb200_last_kernel_variant(void) { return t_variant; }
 
 const char* decxb200_strerror(int code) {
     switch (code) {

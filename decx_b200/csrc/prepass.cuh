@@ -26,9 +26,16 @@ __device__ __forceinline__ float rn_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
+// Finite x whose rounding to tf32 would overflow (|x| within 2^-11 relative of FLT_MAX) keeps the TRUNCATED
+// tf32 value as hi, so hi and lo stay finite.  Non-finite x: hi = x and lo = 0 instead of inf - inf = NaN;
+// the products then give inf or NaN as IEEE does, except that inf times a value whose lo plane is zero
+// yields NaN (inf * 0) where a plain fp32 GEMM would keep inf -- a limit of every split-precision scheme.
 __device__ __forceinline__ void split1(float x, float& hi, float& lo) {
+    const uint32_t xb = __float_as_uint(x);
+    const bool finite = (xb & 0x7f800000u) != 0x7f800000u;
     hi = rn_tf32(x);
-    lo = rn_tf32(x - hi);
+    if (finite && (__float_as_uint(hi) & 0x7f800000u) == 0x7f800000u) hi = __uint_as_float(xb & 0xffffe000u);
+    lo = finite ? rn_tf32(x - hi) : 0.f;
 }
 
 // X: rows x cols (ldx floats per row)  ->  hi, lo: rows x cols (ldw floats per row, ldw % 4 == 0,

@@ -119,7 +119,7 @@ def gemm_raw(dt, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd, alpha=
     return capi.lib.decxb200_last_launch_count()
 
 
-def gemm_fp16_panels(A, B, out, panel_col_end, flags, epoch, status=None, max_ctas=0):
+def gemm_fp16_panels(A, B, out, panel_col_end, flags, epoch, status=None, max_ctas=0, tile=0):
     """One GEMM launch over a B that arrives panel by panel (``decxb200_gemm_fp16_panels``).
 
     ``flags`` is an int32/uint32 CUDA tensor with one word per panel; the stream that fills panel i writes
@@ -131,7 +131,7 @@ def gemm_fp16_panels(A, B, out, panel_col_end, flags, epoch, status=None, max_ct
         code = capi.lib.decxb200_gemm_fp16_panels(
             torch.cuda.current_stream().cuda_stream, M, N, K, A.data_ptr(), _ld(A), B.data_ptr(), _ld(B),
             out.data_ptr(), _ld(out), status.data_ptr() if status is not None else None,
-            len(panel_col_end), ends, flags.data_ptr(), epoch, max_ctas)
+            len(panel_col_end), ends, flags.data_ptr(), epoch, max_ctas, tile)
     capi.check(code)
     return out
 

@@ -183,12 +183,18 @@ void decx::_GPU_Matrix::construct(const de::_DATA_TYPES_FLAGS_ t, uint32_t width
 
 void decx::_GPU_Matrix::re_construct(const de::_DATA_TYPES_FLAGS_ t, uint32_t width, uint32_t height,
                                      decx::cuda_stream* S) {
-    if (_init && t == type && width == _layout.width && height == _layout.height) return;
+    // a block is only kept if it lives in the pool of the device that is current now (the device the caller
+    // is about to launch on) and the pool has not been released under it
+    int now_dev = 0;
+    cudaGetDevice(&now_dev);
+    const bool usable = Mat.block != nullptr && !Mat.block->orphan &&
+                        Mat.block->pool == decx::MemPool_D::GetInstance(now_dev);
+    if (_init && usable && t == type && width == _layout.width && height == _layout.height) return;
     const int es = decx::element_size(t);
     const uint64_t need = uint64_t(decx::pitch_for(width, es, 128)) * height * es;
     type = t;
     fill_layout(_layout, t, width, height, 128);
-    if (_init && Mat.block != nullptr && Mat.block->size >= need && Mat.block->refcount == 1) {
+    if (_init && usable && Mat.block->size >= need && Mat.block->refcount == 1) {
         total_bytes = need;                           // grow-only: the block is kept
         return;
     }

@@ -76,6 +76,7 @@ struct MemBlock {
     bool idle = true;
     int refcount = 0;
     int chunk = -1;             // index of the owning chunk
+    bool orphan = false;        // the pool was released while references were alive: memory gone, metadata kept
     MemBlock* prev = nullptr;   // neighbours inside the chunk, in address order
     MemBlock* next = nullptr;
 };

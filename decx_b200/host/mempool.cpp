@@ -101,6 +101,10 @@ void decx::MemPool_D::merge_with_next(decx::MemBlock* b) {
 void decx::MemPool_D::deallocate(decx::MemBlock* b) {
     if (b == nullptr) return;
     std::lock_guard<std::mutex> lk(_mtx);
+    if (b->orphan) {                      // its chunk went back to CUDA in release(); only the record is left
+        if (--b->refcount <= 0) delete b;
+        return;
+    }
     if (b->idle || --b->refcount > 0) return;
     b->idle = true;
     b->refcount = 0;
@@ -116,7 +120,18 @@ void decx::MemPool_D::release() {
     for (Chunk& c : _chunks) {
         for (decx::MemBlock* b = c.first; b != nullptr;) {
             decx::MemBlock* n = b->next;
-            delete b;
+            if (b->idle) {
+                delete b;
+            } else {
+                // a matrix or scratch object still holds this block (the reference frees only the chunk memory
+                // here, MemoryPool_D.cu:154-166, so releasing such an object later is harmless there): keep the
+                // record so that a later deallocate() finds valid metadata; the last reference deletes it
+                b->orphan = true;
+                b->ptr = nullptr;
+                b->size = 0;
+                b->prev = b->next = nullptr;
+                b->chunk = -1;
+            }
             b = n;
         }
         g_raw_free(c.base);
@@ -193,13 +208,16 @@ int decx::alloc::_device_malloc(decx::PtrInfo<void>* p, uint64_t bytes, bool set
     p->ptr = b->ptr;
     if (set_zero) {
         const cudaError_t e = S ? cudaMemsetAsync(p->ptr, 0, bytes, S->get_raw_stream_ref()) : cudaMemset(p->ptr, 0, bytes);
-        if (e != cudaSuccess) return int(e);
+        if (e != cudaSuccess) {
+            decx::alloc::_device_dealloc(p);      // nothing is handed out on failure
+            return int(e);
+        }
     }
     return 0;
 }
 
 int decx::alloc::_device_realloc(decx::PtrInfo<void>* p, uint64_t bytes, bool set_zero, decx::cuda_stream* S) {
-    if (p->block != nullptr && p->block->size >= bytes && p->block->refcount == 1) {
+    if (p->block != nullptr && !p->block->orphan && p->block->size >= bytes && p->block->refcount == 1) {
         if (set_zero) {
             const cudaError_t e = S ? cudaMemsetAsync(p->ptr, 0, bytes, S->get_raw_stream_ref()) : cudaMemset(p->ptr, 0, bytes);
             if (e != cudaSuccess) return int(e);

@@ -273,7 +273,7 @@ class ShardedGemm:
         capi.check(capi.lib.decxb200_gemm_fp16_panels(
             torch.cuda.current_stream(self.device).cuda_stream, self.nrows, self.N, self.K,
             self.A.data_ptr(), self.A.stride(0), self.Bfull.data_ptr(), self.N, self._d_ptr, self.N,
-            self.status.data_ptr(), len(ends), arr, self.flags.data_ptr(), epoch, self._max_ctas))
+            self.status.data_ptr(), len(ends), arr, self.flags.data_ptr(), epoch, self._max_ctas, 0))
         self.launches += capi.lib.decxb200_last_launch_count()
 
     def compute_only(self):

@@ -76,9 +76,14 @@ DECXB200_API int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, 
 
 /*
  * Same, with the tuning knobs exposed (tests and the benchmark use them):
- *   cta_group: 0 = library default, 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile
+ *   cta_group: one of DECXB200_TILE_*: 0 = library default (a small cost model picks), 1 = one CTA per
+ *              128x256 tile, 2 = CTA pair per 256x256 tile, 3 = CTA pair per 256x512 tile (fp16 only)
  *   max_ctas:  upper bound on the persistent grid (0 = number of SMs)
  */
+#define DECXB200_TILE_AUTO 0
+#define DECXB200_TILE_128x256 1
+#define DECXB200_TILE_256x256 2
+#define DECXB200_TILE_256x512 3
 DECXB200_API int decxb200_gemm_ex(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K,
                                   const void* A, uint64_t lda, const void* B, uint64_t ldb,
                                   const void* C, uint64_t ldc, void* D, uint64_t ldd,
@@ -156,7 +161,7 @@ DECXB200_API int decxb200_ipc_alloc(size_t bytes, void** dptr);
  * fp16 GEMM whose B operand is still arriving (row-sharded multi-GPU GEMM; no counterpart in the
  * single-GPU reference).  B is a full K x N row-major replica in this GPU's memory that another
  * stream fills column panel by column panel (panel i = columns [panel_col_end[i-1], panel_col_end[i]),
- * at most 8 panels, the last end = N, the others multiples of 256).  After panel i's data, that stream
+ * at most 8 panels, the last end = N, the others multiples of 256; of 512 when the 256x512 tile is forced).  After panel i's data, that stream
  * writes `epoch` to panel_flags[i] (decxb200_write_flag_async).  ONE kernel launch computes D = A.B: it
  * walks the tiles panel by panel and its loader waits -- bounded, then status word 0x106 -- for a panel's
  * flag before it touches that panel, so the transfer of B overlaps the tiles of the panels before it.
@@ -166,7 +171,8 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
                                            const void* A, uint64_t lda, const void* B, uint64_t ldb,
                                            void* D, uint64_t ldd, unsigned* status,
                                            uint32_t n_panels, const uint32_t* panel_col_end,
-                                           const unsigned* panel_flags, unsigned epoch, int max_ctas);
+                                           const unsigned* panel_flags, unsigned epoch, int max_ctas,
+                                           int tile /* DECXB200_TILE_AUTO or DECXB200_TILE_256x512 */);
 /* 2-D copy by the copy engines between any two device buffers this process can address (peer mappings
  * included): `rows` rows of `width_bytes`, rows dpitch / spitch bytes apart.  cudaMemcpy2DAsync. */
 DECXB200_API int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch,
@@ -180,6 +186,11 @@ DECXB200_API int decxb200_ipc_close(void* peer_ptr);
 
 /* Number of kernels the last decxb200_gemm* call of this thread launched (pre-passes included). */
 DECXB200_API int decxb200_last_launch_count(void);
+
+/* Which GEMM kernel the last call of this thread launched: 100*KIND + 10*CTAS + NACC
+ * (KIND 0 = fp16, 1 = 3xTF32; CTAS = CTAs per tile; NACC = 256-column accumulators per tile),
+ * e.g. 22 = fp16 256x512 pair tile, 121 = 3xTF32 256x256 pair tile. */
+DECXB200_API int decxb200_last_kernel_variant(void);
 
 /* Static description of an error code returned by this library. */
 DECXB200_API const char* decxb200_strerror(int code);

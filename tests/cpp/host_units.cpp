@@ -147,12 +147,72 @@ static void test_pool() {
     decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
 }
 
+// The pool is released (DECX_CUDA_exit) while objects still hold blocks: their later release / re-shape must
+// not touch freed metadata, and must never hand the stale memory out again.
+static void test_pool_release_under_live_objects() {
+    decx::MemPool_D::set_raw_allocator(fake_alloc, fake_free);
+    decx::MemPool_D* pool = decx::MemPool_D::GetInstance(62);
+    decx::PtrInfo<void> a, b;
+    decx::MemBlock* blk = nullptr;
+    CHECK(pool->allocate(4096, &blk) == 0);
+    a.block = blk; a.ptr = blk->ptr;
+    CHECK(pool->allocate(8192, &blk) == 0);
+    b.block = blk; b.ptr = blk->ptr;
+    decx::alloc::_device_malloc_same_place(&b);             // two holders of b
+    pool->release();
+    CHECK(pool->chunk_count() == 0 && pool->bytes_reserved() == 0);
+    CHECK(a.block->orphan && b.block->orphan && a.block->ptr == nullptr);
+    decx::alloc::_device_dealloc(&a);                       // deletes the orphan record
+    CHECK(a.block == nullptr);
+    decx::PtrInfo<void> b2 = b;
+    decx::alloc::_device_dealloc(&b);                       // first holder
+    // a matrix that still holds the orphan must not reuse it when re-shaped
+    decx::_GPU_Matrix m;
+    m.Mat = b2;
+    m._init = true;
+    m._device = 62;
+    m.type = de::_FP32_;
+    m._layout.width = 8; m._layout.height = 8; m._layout.pitch = 32; m._layout._single_element_size = 4;
+    m.re_construct(de::_FP32_, 8, 8);                       // same shape: used to return early and keep the dead block
+    CHECK(m.Mat.block == nullptr || !m.Mat.block->orphan);
+    m.release();
+    CHECK(pool->check_invariants());
+    decx::MemPool_D::GetInstance(0)->release();
+    decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
+}
+
+// dst was built on another GPU than the one the GEMM is about to run on: its block must go back to ITS pool and
+// must not be written through by a kernel of the current device.
+static void test_reconstruct_never_keeps_another_devices_block() {
+    decx::MemPool_D::set_raw_allocator(fake_alloc, fake_free);
+    decx::MemPool_D* other = decx::MemPool_D::GetInstance(61);
+    decx::MemBlock* blk = nullptr;
+    CHECK(other->allocate(1 << 16, &blk) == 0);
+    decx::_GPU_Matrix m;
+    m.Mat.block = blk; m.Mat.ptr = blk->ptr;
+    m._init = true;
+    m._device = 61;
+    m.type = de::_FP32_;
+    m._layout.width = 64; m._layout.height = 64; m._layout.pitch = 64; m._layout._single_element_size = 4;
+    m.total_bytes = 64 * 64 * 4;
+    CHECK(other->bytes_in_use() == (1u << 16));
+    m.re_construct(de::_FP32_, 64, 64);                     // current device is 0 (or none): not pool 61
+    CHECK(other->bytes_in_use() == 0);                      // the old block went home
+    CHECK(m.Mat.block == nullptr || m.Mat.block->pool != other);
+    m.release();
+    other->release();
+    decx::MemPool_D::GetInstance(0)->release();
+    decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
+}
+
 int main() {
     test_abi();
     test_pitch_and_host_matrix();
     test_half();
     test_errors();
     test_pool();
+    test_pool_release_under_live_objects();
+    test_reconstruct_never_keeps_another_devices_block();
     if (g_fail == 0) std::printf("host_units: all checks passed\n");
     return g_fail == 0 ? 0 : 1;
 }

@@ -233,3 +233,15 @@ def test_host_pointer_entry_point(G, dev, dt, pinned):
     D = G.gemm(gA.view, gB.view, gC.view, alpha, beta)
     torch.cuda.synchronize()
     assert torch.equal(D.cpu(), out[:, :N])
+
+
+def test_huge_finite_fp32_inputs_do_not_turn_into_nan(G, dev):
+    """Values next to FLT_MAX: rounding them up to tf32 would overflow; the split keeps them finite."""
+    rng = np.random.default_rng(12)
+    A = rng.uniform(-1, 1, (70, 40)).astype(np.float32)
+    B = rng.uniform(-1e-3, 1e-3, (40, 50)).astype(np.float32)
+    fmax = np.finfo(np.float32).max
+    A[3, 5], A[10, 0], A[69, 39] = fmax, -fmax, 3.4e38
+    D = _run(G, dev, A, B)
+    assert np.isfinite(D).all()
+    _check(D, A, B)

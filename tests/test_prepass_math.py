@@ -11,9 +11,29 @@ def rn_tf32(x):
 
 
 def split(x):
-    hi = rn_tf32(x)
-    lo = rn_tf32((np.asarray(x, dtype=np.float32) - hi).astype(np.float32))
-    return hi, lo
+    """split1 of prepass.cuh: hi = rn_tf32(x) (truncated instead when the rounding would overflow a finite x),
+    lo = rn_tf32(x - hi), and lo = 0 for a non-finite x."""
+    x = np.asarray(x, dtype=np.float32)
+    finite = np.isfinite(x)
+    with np.errstate(over="ignore", invalid="ignore"):
+        hi = rn_tf32(x)
+        over = finite & ~np.isfinite(hi)
+        hi = np.where(over, (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32), hi)
+        lo = np.where(finite, rn_tf32((x - hi).astype(np.float32)), np.float32(0))
+    return hi.astype(np.float32), lo.astype(np.float32)
+
+
+def test_split_of_huge_and_non_finite_values():
+    fmax = np.finfo(np.float32).max
+    x = np.array([fmax, -fmax, np.nextafter(np.float32(fmax), np.float32(0)), 3.0e38, np.inf, -np.inf, np.nan],
+                 dtype=np.float32)
+    hi, lo = split(x)
+    fin = np.isfinite(x)
+    assert np.isfinite(hi[fin]).all() and np.isfinite(lo[fin]).all()       # no overflow from the rounding of hi
+    assert (hi[fin].astype(np.float64) + lo[fin].astype(np.float64) == x[fin].astype(np.float64)).all() or \
+        (np.abs(hi[fin].astype(np.float64) + lo[fin].astype(np.float64) - x[fin]) <= np.abs(x[fin]) * 2.0 ** -21).all()
+    assert hi[4] == np.inf and hi[5] == -np.inf and np.isnan(hi[6])
+    assert (lo[4:] == 0).all()                                             # inf stays inf, never inf - inf
 
 
 def test_split_planes_are_tf32_exact_and_close():
