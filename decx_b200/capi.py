@@ -19,6 +19,13 @@ class DecxB200Error(RuntimeError):
         self.code = code
 
 
+class FetchJob(ctypes.Structure):
+    """``decxb200_fetch_job``: one piece of B a GPU brings into its replica while the GEMM runs."""
+    _fields_ = [("src", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("row0", ctypes.c_uint32),
+                ("rows", ctypes.c_uint32), ("col0", ctypes.c_uint32), ("cols", ctypes.c_uint32),
+                ("panel", ctypes.c_uint32), ("publish", ctypes.c_uint32)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -42,6 +49,11 @@ def _load():
     lib.decxb200_gemm_fp16_panels.restype = ci
     lib.decxb200_gemm_fp16_panels.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32,
                                               ctypes.POINTER(u32), vp, ctypes.c_uint, ci, ci]
+    lib.decxb200_fetch_scratch_bytes.restype = sz
+    lib.decxb200_fetch_scratch_bytes.argtypes = [u32]
+    lib.decxb200_gemm_fp16_fetch.restype = ci
+    lib.decxb200_gemm_fp16_fetch.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32, ctypes.POINTER(u32),
+                                             vp, vp, ctypes.c_uint, ctypes.POINTER(FetchJob), u32, vp, sz, ci, ci]
     lib.decxb200_copy2d_async.restype = ci
     lib.decxb200_copy2d_async.argtypes = [vp, vp, sz, vp, sz, sz, sz]
     lib.decxb200_write_flag_async.restype = ci
@@ -74,7 +86,7 @@ EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
     "decxb200_gemm_fp32_noalloc",
-    "decxb200_gemm_fp16_panels", "decxb200_copy2d_async", "decxb200_write_flag_async",
+    "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_strerror", "decxb200_version",
 ]

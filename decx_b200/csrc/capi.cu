@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/decx_b200.h"
 #include "gemm_sm100.cuh"
@@ -35,7 +36,7 @@ constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
     unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
-    bool attr_set[2][2][2] = {};
+    bool attr_set[2][2][2][2] = {};
 };
 DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
@@ -84,9 +85,9 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
-template <int KIND, int CTAS, int NACC = 1>
+template <int KIND, int CTAS, int NACC = 1, int FETCH = 0>
 int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                const CUtensorMap& b1, GemmParams p, int max_ctas) {
+                const CUtensorMap& b1, GemmParams p, int max_ctas, const FetchParams* fetch = nullptr) {
     // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
     // that is what makes the stores efficient when D lives in another GPU's memory; DECXB200_TMA_STORE=0 disables
     static const int tma_store_env = [] { const char* e = getenv("DECXB200_TMA_STORE"); return e ? atoi(e) : 1; }();
@@ -96,8 +97,11 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
         const bool f16 = (KIND == 0);
         if (make_map(&dmap, f16, p.D, p.M, p.N, p.ldd, f16 ? 64 : 32, 32) == 0) p.d_tma = 1;
     }
-    using Cfg = GemmCfg<KIND, CTAS, NACC>;
-    auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC>;
+    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
+    auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC, FETCH>;
+    FetchParams f;
+    memset(&f, 0, sizeof(f));
+    if (fetch != nullptr) f = *fetch;
     DeviceInfo& di = g_dev[dev];
     {
         std::lock_guard<std::mutex> lk(g_dev_mutex);
@@ -105,10 +109,10 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
             cudaError_t e = cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess) return int(e);
         }
-        if (!di.attr_set[KIND][CTAS - 1][NACC - 1]) {
+        if (!di.attr_set[KIND][CTAS - 1][NACC - 1][FETCH ? 1 : 0]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
             if (e != cudaSuccess) return int(e);
-            di.attr_set[KIND][CTAS - 1][NACC - 1] = true;
+            di.attr_set[KIND][CTAS - 1][NACC - 1][FETCH ? 1 : 0] = true;
         }
     }
     p.tiles_m = uint32_t((uint64_t(p.M) + Cfg::BM * CTAS - 1) / (Cfg::BM * CTAS));
@@ -130,7 +134,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     uint32_t workers = uint32_t(di.sm_count / CTAS);
     if (max_ctas > 0 && uint32_t(max_ctas / CTAS) < workers) workers = uint32_t(max_ctas / CTAS);
     if (workers == 0) workers = 1;
-    if (tiles < workers) workers = uint32_t(tiles);
+    if (tiles < workers && FETCH == 0) workers = uint32_t(tiles);      // couriers want every SM, tiles or not
     // group height: balance the A rows and B columns the concurrently running tiles touch
     uint32_t g = (CTAS == 1) ? 16 : (NACC == 2 ? 12 : 8);
     if (const char* e = getenv("DECXB200_GROUP_M")) {       // tuning override
@@ -163,10 +167,10 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, p, f);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
-    t_variant = KIND * 100 + CTAS * 10 + NACC;
+    t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0);
     return 0;
 }
 
@@ -286,7 +290,8 @@ struct PanelGate {            // B arrives in column panels while the kernel run
 
 int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
             const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc,
-            unsigned* status, int cta_group, int max_ctas, const PanelGate* gate = nullptr) {
+            unsigned* status, int cta_group, int max_ctas, const PanelGate* gate = nullptr,
+            const FetchParams* fetch = nullptr) {
     if ((lda % 8) != 0 || (ldb % 8) != 0 || !aligned16(A) || !aligned16(B)) return DECXB200_EALIGN;
     GemmParams p;
     fill_common(p, sc, C, D, status);
@@ -347,6 +352,11 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc != 0) return rc;
+    if (fetch != nullptr) {
+        if (cta_group != 2) return DECXB200_EINVAL;
+        return nacc == 2 ? launch_gemm<0, 2, 2, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas, fetch)
+                         : launch_gemm<0, 2, 1, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas, fetch);
+    }
     if (nacc == 2) return launch_gemm<0, 2, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
     return cta_group == 1 ? launch_gemm<0, 1>(stream, dev, a0, a0, b0, b0, p, max_ctas)
                           : launch_gemm<0, 2>(stream, dev, a0, a0, b0, b0, p, max_ctas);
@@ -688,6 +698,82 @@ int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K,
     g.epoch = epoch;
     return run_f16(reinterpret_cast<cudaStream_t>(stream_), dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(),
                    status, cta_group, max_ctas, &g);
+}
+
+size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) { return 256 + size_t(n_jobs) * sizeof(FetchJob); }
+
+int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, void* B,
+                             uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
+                             const uint32_t* panel_col_end, unsigned* ready_flags, unsigned* pub_flags, unsigned epoch,
+                             const decxb200_fetch_job* jobs, uint32_t n_jobs, void* scratch, size_t scratch_bytes,
+                             int max_ctas, int tile) {
+    t_launches = 0;
+    int dev = 0, cta_group = (tile == DECXB200_TILE_256x512) ? tile : 2;
+    int rc = check_common(DECXB200_FP16, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, cta_group, dev);
+    if (rc != 0) return rc;
+    if (n_panels == 0 || n_panels > uint32_t(MAX_PANELS) || panel_col_end == nullptr) return DECXB200_EINVAL;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    PanelGate g;
+    g.n = n_panels;
+    uint32_t prev = 0;
+    for (uint32_t i = 0; i < n_panels; ++i) {
+        if (panel_col_end[i] <= prev || panel_col_end[i] > N) return DECXB200_EINVAL;
+        g.col_end[i] = prev = panel_col_end[i];
+    }
+    if (prev != N) return DECXB200_EINVAL;
+    g.flags = ready_flags;
+    g.epoch = epoch;
+    if (n_jobs == 0) {
+        // nothing to bring in (this GPU already holds all of B): the plain or the flag-gated GEMM
+        return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas,
+                       ready_flags != nullptr ? &g : nullptr);
+    }
+    if (jobs == nullptr || ready_flags == nullptr || pub_flags == nullptr || scratch == nullptr ||
+        scratch_bytes < decxb200_fetch_scratch_bytes(n_jobs) || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0)
+        return DECXB200_EWORKSPACE;
+    FetchParams f;
+    memset(&f, 0, sizeof(f));
+    std::vector<FetchJob> table(n_jobs);
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        const decxb200_fetch_job& j = jobs[i];
+        if (j.panel >= n_panels || (j.col0 % 8) != 0 || (j.cols % 8) != 0 || j.cols == 0) return DECXB200_EINVAL;
+        const uint32_t lo = j.panel ? g.col_end[j.panel - 1] : 0u;
+        if (j.col0 < lo || uint64_t(j.col0) + j.cols > g.col_end[j.panel]) return DECXB200_EINVAL;
+        if (uint64_t(j.row0) + j.rows > K) return DECXB200_EINVAL;
+        if (j.rows != 0 && (j.src == nullptr || !aligned16(j.src))) return DECXB200_EINVAL;
+        if (j.rows == 0 && j.gate == nullptr) return DECXB200_EINVAL;     // a piece nobody delivers and nobody flags
+        FetchJob& t = table[i];
+        t.src = static_cast<const uint8_t*>(j.src);
+        t.gate = j.gate;
+        t.row0 = j.row0; t.rows = j.rows;
+        t.byte0 = j.col0 * 2; t.bytes = j.cols * 2;
+        t.panel = j.panel;
+        t.publish = j.publish ? 1u : 0u;
+        const uint32_t nb = fetch_job_batches(t.rows, t.bytes);
+        f.need[t.panel] += nb;
+        if (t.publish) f.pub_need[t.panel] += nb;
+        f.total_batches += nb;
+    }
+    for (uint32_t i = 0; i < n_panels; ++i)
+        if (f.need[i] == 0) return DECXB200_EINVAL;       // a panel nothing delivers would never be flagged
+    uint8_t* sc = static_cast<uint8_t*>(scratch);
+    cudaError_t e;
+    if ((e = cudaMemsetAsync(sc, 0, 256, stream)) != cudaSuccess) return int(e);
+    // pageable source: staged by the runtime before the call returns, so `table` may go out of scope
+    if ((e = cudaMemcpyAsync(sc + 256, table.data(), size_t(n_jobs) * sizeof(FetchJob), cudaMemcpyHostToDevice,
+                             stream)) != cudaSuccess)
+        return int(e);
+    f.jobs = reinterpret_cast<const FetchJob*>(sc + 256);
+    f.n_jobs = n_jobs;
+    f.dst = static_cast<uint8_t*>(B);
+    f.pitch = ldb * 2;
+    f.arrived = reinterpret_cast<unsigned*>(sc);
+    f.published = reinterpret_cast<unsigned*>(sc + 64);
+    f.ready_flags = ready_flags;
+    f.pub_flags = pub_flags;
+    f.epoch = epoch;
+    return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas, &g,
+                   &f);
 }
 
 int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes,

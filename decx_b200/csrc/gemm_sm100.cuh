@@ -44,6 +44,14 @@
 //         [.. + 128 h, +128) of both CTAs.  Both TMEM accumulators belong to one tile, so the epilogue
 //         (eight warps, four per accumulator) no longer overlaps the next tile's MMAs: used for long K.
 //
+// FETCH f (fp16 pairs, row-sharded multi-GPU GEMM) adds f "courier" warps per CTA that bring B into this GPU's
+//         memory WHILE the tiles are computed: they walk a job list (source address in a peer GPU's memory,
+//         rows, column range, an optional gate word), copy 8 KB batches with 16-byte peer loads and local
+//         stores, count the batches per column panel and raise that panel's flag when it is complete -- the flag
+//         the TMA producer waits on.  Pieces this GPU is the first holder of are "published" through a second
+//         flag that the other GPUs' couriers gate on, so one kernel per GPU does scatter + all-gather of B,
+//         the product and (through D in the owner's memory) the gather.  All TMA loads still read local memory.
+//
 // Ragged M/N/K: tensor maps carry the logical extents, so out-of-range parts of a box
 // are zero-filled by TMA on loads and dropped on stores.  No host-side padding.
 // Every wait is bounded: on time-out the role writes a code to *status and unwinds.
@@ -64,8 +72,9 @@ enum KernelStatus : unsigned {
     KS_TIMEOUT_EPILOGUE = 0x104,
     KS_TIMEOUT_TAIL = 0x105,
     KS_TIMEOUT_PANEL = 0x106,
+    KS_TIMEOUT_FETCH = 0x107,
 };
-constexpr int MAX_PANELS = 8;
+constexpr int MAX_PANELS = 16;
 
 struct GemmParams {
     uint32_t M, N, K;          // real problem extents seen by the MMA (complex: N, K doubled)
@@ -97,6 +106,37 @@ struct GemmParams {
     unsigned sync_limit_ns;    // how long a producer waits for the others before it goes on alone
 };
 
+// One piece of B a courier warp copies into this GPU's replica: rows [row0, row0 + rows) x bytes [byte0, byte0 +
+// bytes) of every row, from `src` (same row pitch as the replica; usually another GPU's memory).  rows == 0 is a
+// piece something else delivers (a copy engine): the courier only waits for its gate and counts it.
+struct FetchJob {
+    const uint8_t* src;
+    const unsigned* gate;      // word that must have reached `epoch` before src may be read; nullptr: readable now
+    uint32_t row0, rows;
+    uint32_t byte0, bytes;     // bytes % 16 == 0
+    uint32_t panel;            // column panel the piece belongs to
+    uint32_t publish;          // 1: other GPUs fetch this piece from here once it has landed (pub_flags)
+};
+constexpr uint32_t FETCH_UNROLL = 16;                   // 512-byte segments per batch (one warp, one go): 8 KB
+__host__ __device__ inline uint32_t fetch_job_batches(uint32_t rows, uint32_t bytes) {
+    const uint64_t segs = uint64_t(rows) * ((bytes + 511u) / 512u);
+    return segs == 0 ? 1u : uint32_t((segs + FETCH_UNROLL - 1) / FETCH_UNROLL);
+}
+struct FetchParams {
+    const FetchJob* jobs;      // device memory
+    uint32_t n_jobs;
+    uint32_t total_batches;    // sum of fetch_job_batches over the jobs
+    uint8_t* dst;              // this GPU's replica of B
+    uint64_t pitch;            // bytes per row, source and destination
+    unsigned* arrived;         // [MAX_PANELS] batches stored so far, zero at launch
+    unsigned* published;       // [MAX_PANELS] batches of publishing jobs stored so far, zero at launch
+    unsigned* ready_flags;     // [MAX_PANELS] <- epoch when every batch of the panel is stored (= GemmParams::panel_flags)
+    unsigned* pub_flags;       // [MAX_PANELS] <- epoch when every publishing batch of the panel is stored
+    unsigned epoch;
+    uint32_t need[MAX_PANELS];       // batches per panel
+    uint32_t pub_need[MAX_PANELS];   // publishing batches per panel (0: nothing to publish)
+};
+
 // Ticket counter of the soft tile barrier.  All CTAs of a launch are resident at once (one per SM), and
 // they share A row slabs and B column slabs through L2 only while they walk K at the same pace; left
 // alone they drift apart and the slabs are fetched from HBM again and again.  So before a producer
@@ -107,9 +147,10 @@ struct GemmParams {
 __device__ unsigned g_wave_ticket;
 
 
-template <int KIND, int CTAS, int NACC = 1>
+template <int KIND, int CTAS, int NACC = 1, int FETCH = 0>
 struct GemmCfg {
     static_assert(NACC == 1 || (NACC == 2 && KIND == 0 && CTAS == 2), "two accumulators per tile: fp16 CTA pairs only");
+    static_assert(FETCH == 0 || (KIND == 0 && CTAS == 2), "courier warps: fp16 CTA pairs only");
     static constexpr int ELEM = (KIND == 0) ? 2 : 4;
     static constexpr int NPL = (KIND == 0) ? 1 : 2;       // operand planes (hi, lo)
     static constexpr int BM = 128;                        // rows per CTA
@@ -131,7 +172,7 @@ struct GemmCfg {
     static constexpr int EPI_WARPS = PROMOTE ? 8 : 4 * NACC;
     static constexpr int EPI_COLS = PROMOTE ? BN / 2 : BN;   // accumulator columns per epilogue thread
     static constexpr int ACC_ARRIVALS = (EPI_WARPS / NACC) * CTAS;   // epilogue warps (of the pair) per accumulator
-    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * FETCH;
     static constexpr int STAGING = EPI_WARPS * 4096;      // per epilogue warp: 32 rows x 128 bytes of output
     static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
@@ -287,12 +328,85 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
     }
 }
 
-template <int KIND, int CTAS, int NACC>
-__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC>::THREADS, 1)
+// Courier warp `courier` of `n_couriers` (all CTAs of the grid together): copies its share of the job list's
+// batches, in list order, into the local replica and keeps the per-panel counts.  Every wait is bounded.
+__device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParams& p, uint32_t courier,
+                                           uint32_t n_couriers, uint32_t lane) {
+    uint32_t job = 0, job_first = 0;             // first batch index of `job`
+    uint32_t spr = 0, nseg = 0, nb = 0;
+    FetchJob J;
+    bool have = false, gate_open = false;
+    for (uint32_t b = courier; b < f.total_batches; b += n_couriers) {
+        for (;;) {                               // the job that holds batch b (batches only move forward)
+            if (!have) {
+                if (job >= f.n_jobs) return;     // inconsistent table: stop rather than read past it
+                J = f.jobs[job];
+                spr = (J.bytes + 511u) / 512u;
+                nseg = J.rows * spr;
+                nb = fetch_job_batches(J.rows, J.bytes);
+                have = true;
+                gate_open = (J.gate == nullptr);
+            }
+            if (b < job_first + nb) break;
+            job_first += nb;
+            ++job;
+            have = false;
+        }
+        if (!gate_open) {
+            // the piece is being produced elsewhere (another GPU's couriers or a copy engine): wait for its flag
+            uint32_t ok = 1;
+            if (lane == 0) {
+                const uint64_t t0 = global_timer_ns();
+                while (int(ld_acquire_sys(J.gate) - f.epoch) < 0) {
+                    if (global_timer_ns() - t0 > p.wait_limit_ns) { ok = 0; break; }
+                    __nanosleep(256);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) report(p, KS_TIMEOUT_FETCH);
+                return;
+            }
+            (void)ld_acquire_sys(J.gate);        // every lane orders its own loads of the piece after the flag
+            gate_open = true;
+        }
+        const uint32_t g0 = (b - job_first) * FETCH_UNROLL;
+        uint32_t row = g0 / (spr ? spr : 1u), cs = g0 - row * spr;
+        uint4 v[FETCH_UNROLL];
+        uint64_t off[FETCH_UNROLL];
+#pragma unroll
+        for (uint32_t u = 0; u < FETCH_UNROLL; ++u) {
+            const uint32_t colb = cs * 512u + lane * 16u;
+            const bool valid = (g0 + u < nseg) && (colb < J.bytes);
+            off[u] = valid ? (uint64_t(J.row0 + row) * f.pitch + J.byte0 + colb) : ~0ull;
+            if (valid) v[u] = ld_volatile_v4(J.src + off[u]);
+            if (++cs == spr) { cs = 0; ++row; }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
+            if (off[u] != ~0ull) *reinterpret_cast<uint4*>(f.dst + off[u]) = v[u];
+        // the stores of every lane are performed before the counts below can be seen to include this batch
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+            if (atomicAdd(f.arrived + J.panel, 1u) + 1u == f.need[J.panel]) {
+                __threadfence_system();
+                st_release_sys(f.ready_flags + J.panel, f.epoch);
+            }
+            if (J.publish && atomicAdd(f.published + J.panel, 1u) + 1u == f.pub_need[J.panel]) {
+                __threadfence_system();
+                st_release_sys(f.pub_flags + J.panel, f.epoch);
+            }
+        }
+    }
+}
+
+template <int KIND, int CTAS, int NACC, int FETCH>
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                    const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
-    using Cfg = GemmCfg<KIND, CTAS, NACC>;
+                    const __grid_constant__ CUtensorMap tmD, const GemmParams p, const FetchParams f) {
+    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
@@ -516,6 +630,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 }
             }
         }
+    } else if (FETCH > 0 && warp >= 2u + Cfg::EPI_WARPS) {
+        // ------------------------------------------------------------------ couriers (B from the other GPUs)
+        fetch_role(f, p, blockIdx.x * FETCH + (warp - 2u - Cfg::EPI_WARPS), gridDim.x * FETCH, lane);
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..)
         const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
@@ -648,7 +765,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
     }
 
-    if (warp >= 2 && lane == 0 && p.d_tma) bulk_wait_all();   // this thread's output boxes are in memory
+    if (warp >= 2 && warp < 2u + Cfg::EPI_WARPS && lane == 0 && p.d_tma) bulk_wait_all();   // this thread's output boxes are in memory
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();

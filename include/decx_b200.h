@@ -161,7 +161,7 @@ DECXB200_API int decxb200_ipc_alloc(size_t bytes, void** dptr);
  * fp16 GEMM whose B operand is still arriving (row-sharded multi-GPU GEMM; no counterpart in the
  * single-GPU reference).  B is a full K x N row-major replica in this GPU's memory that another
  * stream fills column panel by column panel (panel i = columns [panel_col_end[i-1], panel_col_end[i]),
- * at most 8 panels, the last end = N, the others multiples of 256; of 512 when the 256x512 tile is forced).  After panel i's data, that stream
+ * at most 16 panels, the last end = N, the others multiples of 256; of 512 when the 256x512 tile is forced).  After panel i's data, that stream
  * writes `epoch` to panel_flags[i] (decxb200_write_flag_async).  ONE kernel launch computes D = A.B: it
  * walks the tiles panel by panel and its loader waits -- bounded, then status word 0x106 -- for a panel's
  * flag before it touches that panel, so the transfer of B overlaps the tiles of the panels before it.
@@ -173,6 +173,44 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
                                            uint32_t n_panels, const uint32_t* panel_col_end,
                                            const unsigned* panel_flags, unsigned epoch, int max_ctas,
                                            int tile /* DECXB200_TILE_AUTO or DECXB200_TILE_256x512 */);
+/*
+ * The same product with the transfer of B fused into the kernel (row-sharded multi-GPU GEMM, one call per GPU;
+ * no counterpart in the single-GPU reference).  `B` is this GPU's replica of the K x N operand; at the call it
+ * may hold nothing yet.  Besides its loader, MMA and epilogue warps every CTA runs "courier" warps that walk
+ * `jobs` in order: each job is a piece of B (rows x columns of one panel) that lies, or will lie, in memory
+ * this GPU can address -- the owner's B or another GPU's replica, both laid out like the local one (row pitch
+ * ldb) -- and is copied into the replica with 16-byte peer loads.  Pieces are counted per panel; when a panel is
+ * complete its word in ready_flags is set to `epoch` and the tiles of that panel start.  A job with
+ * publish = 1 is a piece this GPU is the first to hold outside the owner: once all publishing pieces of a
+ * panel have landed, pub_flags[panel] is set to `epoch`, and the other GPUs' jobs name that word as their
+ * `gate`.  So the owner sends every byte of B once (scatter) and the GPUs complete each other (all-gather),
+ * inside the same launch that multiplies and that stores D into the owner's memory.
+ *
+ *   jobs:      HOST array, copied by the call.  gate == NULL: the source is readable now.  rows == 0: a piece
+ *              that something else writes into the replica (a copy engine); the courier only waits for its
+ *              gate and counts it.  Every panel needs at least one job.  col0, cols: multiples of 8.
+ *   scratch:   device memory, 256-byte aligned, decxb200_fetch_scratch_bytes(n_jobs) bytes (counters + job table).
+ *   ready_flags, pub_flags: device words, one per panel; other GPUs must be able to read pub_flags.
+ *   n_jobs == 0: this GPU already holds B (the owner); ready_flags may then be NULL (no gating at all).
+ *   All waits are bounded: status 0x106 (a panel never completed) or 0x107 (a gate never opened).
+ *   Epochs must increase from one use of the flags to the next.
+ */
+typedef struct decxb200_fetch_job {
+    const void* src;
+    const unsigned* gate;
+    uint32_t row0, rows;
+    uint32_t col0, cols;
+    uint32_t panel;
+    uint32_t publish;
+} decxb200_fetch_job;
+DECXB200_API size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs);
+DECXB200_API int decxb200_gemm_fp16_fetch(void* stream, uint32_t M, uint32_t N, uint32_t K,
+                                          const void* A, uint64_t lda, void* B, uint64_t ldb,
+                                          void* D, uint64_t ldd, unsigned* status,
+                                          uint32_t n_panels, const uint32_t* panel_col_end,
+                                          unsigned* ready_flags, unsigned* pub_flags, unsigned epoch,
+                                          const decxb200_fetch_job* jobs, uint32_t n_jobs,
+                                          void* scratch, size_t scratch_bytes, int max_ctas, int tile);
 /* 2-D copy by the copy engines between any two device buffers this process can address (peer mappings
  * included): `rows` rows of `width_bytes`, rows dpitch / spitch bytes apart.  cudaMemcpy2DAsync. */
 DECXB200_API int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch,
