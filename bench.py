@@ -181,6 +181,50 @@ def run_reference(args, rank, world, emit):
     emit(line)
 
 
+def check_parity(torch, dist, sg, workload, rank, world, device):
+    """After the timed steps: the owner compares sampled rows of D -- first and last row and a tile edge of every
+    rank's shard plus random ones -- with the CPU oracle on the same rows of A (regenerated from their seed) and
+    the same B.  Returns the record for the JSON line; the run fails when the metric exceeds the tolerance."""
+    import numpy as np
+    dtype, M, N, K, dist_name, sigma, fused, ff = WORKLOADS[workload]
+    tol = 1e-2 if dtype == "float16" else 1e-5
+    rec = None
+    if rank == 0:
+        from oracle import binding as ob
+        rng = np.random.default_rng(123)
+        a_rows, d_rows, picked = [], [], 0
+        per_rank = max(4, 32 // world)
+        for r, (r0, n) in enumerate(sg.rows):
+            if n == 0:
+                continue
+            local = sorted({0, n - 1, min(255, n - 1), min(256, n - 1)} | {int(x) for x in rng.integers(0, n, per_rank - 4)})
+            shard = sg.A if r == rank else gen(torch, (n, K), dtype, dist_name, sigma, device, 4 + 1000 * r)
+            a_rows.append(shard[local].cpu())
+            d_rows.append(sg.D[[r0 + i for i in local]].cpu())
+            picked += len(local)
+            del shard
+        A_s, D_s, B_h = torch.cat(a_rows).numpy(), torch.cat(d_rows).numpy(), sg.B.cpu().numpy()
+        m = float(ob.metric(D_s, ob.gemm(A_s, B_h), A_s, B_h))
+        rec = {"metric": m, "rows": picked, "tol": tol, "ok": bool(m <= tol),
+               "against": "oracle/gemm_oracle.c (fp32-accumulating restatement) on the sampled rows"
+               if dtype == "float16" else "oracle/gemm_oracle.c (fp64) on the sampled rows"}
+    if world > 1:
+        dist.barrier()
+    if rec is not None and not rec["ok"]:
+        raise SystemExit(f"parity check failed: metric {rec['metric']:.3e} > {tol} on {rec['rows']} sampled rows")
+    return rec
+
+
+def variant_name(v):
+    """decxb200_last_kernel_variant() -> the kernel's template name."""
+    if not v:
+        return None
+    fetch, v = divmod(v, 1000)
+    kind, rest = divmod(v, 100)
+    ctas, nacc = divmod(rest, 10)
+    return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}>"
+
+
 def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
     """Kernel-level timing of one single-GPU configuration (device-resident operands)."""
     dtype, M, N, K, dist_name, sigma, fused, ff = WORKLOADS[workload]
@@ -220,7 +264,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--panels", default="ramp", help="column panels of B in the sharded path: a count or 'ramp'")
     ap.add_argument("--bcast", default=None, choices=[None, "p2p", "broadcast", "scatter_allgather"])
-    ap.add_argument("--overlap", default=None, choices=[None, "single", "panels"])
+    ap.add_argument("--overlap", default=None, choices=[None, "fused", "single", "panels"])
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--kernel-only", action="store_true",
@@ -316,8 +360,12 @@ def main():
     step_ms = total_ms / args.steps
     value = flops * args.steps / (total_ms * 1e-3) / 1e12
     assert int(sg.status.item()) == 0, f"kernel status {int(sg.status.item()):#x}"
+    parity = check_parity(torch, dist, sg, args.workload, rank, world, device)       # outside the timed region
     total_launches = int(max_over_ranks(float(launches)) * world) if world > 1 else launches
 
+    step_variant = capi.lib.decxb200_last_kernel_variant()      # the kernel the timed steps launched on this rank
+    if world > 1:                                               # the owner fetches nothing: report a fetching rank's kernel
+        step_variant = int(max_over_ranks(float(getattr(sg, "kernel_variant", 0) or step_variant)))
     # dominant kernel alone (no communication): CUDA events around this rank's GEMM launches
     kern_ms = []
     n_launch = 1
@@ -332,6 +380,7 @@ def main():
             e1.record()
             torch.cuda.synchronize(device)
             kern_ms.append(e0.elapsed_time(e1) / max(n_launch, 1))
+    kernel_variant = capi.lib.decxb200_last_kernel_variant()
     barrier()
     flops_per_launch = flops / world / max(n_launch, 1)
     kern_avg = max_over_ranks(sum(kern_ms) / len(kern_ms) if kern_ms else 0.0)
@@ -407,13 +456,14 @@ def main():
                         "of_sustained": (100 * value / (world * pk["bf16_sustained"] / (1 if dtype == "float16" else 6))) if pk["bf16_sustained"] else None},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, world)),
-                     "kernel": "gemm_tcgen05_kernel<0,2,2>" if dtype == "float16" else "gemm_tcgen05_kernel<1,2,1>",
+                     "kernel": variant_name(kernel_variant), "step_kernel": variant_name(step_variant),
                      "launch_ms": kern_avg, "flops_per_launch": flops_per_launch,
                      "peak_source": f"{pk['source']}: bf16 burst {pk['bf16']} TFLOP/s" + ("" if dtype == "float16" else " /6 (TF32 rate, three MMAs per product)")},
         "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3 if e2e_s else None, "how": "decxb200_gemm_host (pinned host A, B, D; copies pipelined with the GEMM)" if world == 1
                 else "pinned host A shards / B / D, copies + sharded step + D to host on the owner"},
         "gpu_launches": total_launches,
+        "parity": parity,
         "clocks": clocks,
     }
     if world == 1 and not args.no_extras:

@@ -286,6 +286,7 @@ struct PanelGate {            // B arrives in column panels while the kernel run
     uint32_t col_end[MAX_PANELS] = {0};
     const unsigned* flags = nullptr;
     unsigned epoch = 0;
+    unsigned long long* stats = nullptr;
 };
 
 int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
@@ -305,6 +306,7 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
         for (uint32_t i = 0; i < gate->n; ++i) p.panel_end[i] = gate->col_end[i];
         p.panel_flags = gate->flags;
         p.panel_epoch = gate->epoch;
+        p.stats = gate->stats;
     }
     using C1 = GemmCfg<0, 1>;
     CUtensorMap a0, b0;
@@ -700,7 +702,9 @@ int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K,
                    status, cta_group, max_ctas, &g);
 }
 
-size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) { return 256 + size_t(n_jobs) * sizeof(FetchJob); }
+// scratch layout: [0, 256) batch counters, [256, 512) timing record (32 x u64), [512, ...) job table
+constexpr size_t FETCH_TABLE_OFF = 512;
+size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) { return FETCH_TABLE_OFF + size_t(n_jobs) * sizeof(FetchJob); }
 
 int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, void* B,
                              uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
@@ -758,12 +762,13 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
         if (f.need[i] == 0) return DECXB200_EINVAL;       // a panel nothing delivers would never be flagged
     uint8_t* sc = static_cast<uint8_t*>(scratch);
     cudaError_t e;
-    if ((e = cudaMemsetAsync(sc, 0, 256, stream)) != cudaSuccess) return int(e);
+    if ((e = cudaMemsetAsync(sc, 0, FETCH_TABLE_OFF, stream)) != cudaSuccess) return int(e);
     // pageable source: staged by the runtime before the call returns, so `table` may go out of scope
-    if ((e = cudaMemcpyAsync(sc + 256, table.data(), size_t(n_jobs) * sizeof(FetchJob), cudaMemcpyHostToDevice,
+    if ((e = cudaMemcpyAsync(sc + FETCH_TABLE_OFF, table.data(), size_t(n_jobs) * sizeof(FetchJob), cudaMemcpyHostToDevice,
                              stream)) != cudaSuccess)
         return int(e);
-    f.jobs = reinterpret_cast<const FetchJob*>(sc + 256);
+    f.jobs = reinterpret_cast<const FetchJob*>(sc + FETCH_TABLE_OFF);
+    g.stats = reinterpret_cast<unsigned long long*>(sc + 256);
     f.n_jobs = n_jobs;
     f.dst = static_cast<uint8_t*>(B);
     f.pitch = ldb * 2;

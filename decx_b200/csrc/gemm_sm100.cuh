@@ -104,6 +104,10 @@ struct GemmParams {
     unsigned sync_base;        // value of the ticket counter when this launch starts
     unsigned sync_on;          // 0 = off
     unsigned sync_limit_ns;    // how long a producer waits for the others before it goes on alone
+    // optional timing record (device memory, zeroed by the host; nullptr = off), in ns of %globaltimer:
+    //   [0..15] when panel i was complete (couriers), [16] start of CTA 0, [17] latest CTA end,
+    //   [18] sum over the loaders of the time spent waiting for panel flags, [19] number of such waits
+    unsigned long long* stats;
 };
 
 // One piece of B a courier warp copies into this GPU's replica: rows [row0, row0 + rows) x bytes [byte0, byte0 +
@@ -330,16 +334,46 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
 
 // Courier warp `courier` of `n_couriers` (all CTAs of the grid together): copies its share of the job list's
 // batches, in list order, into the local replica and keeps the per-panel counts.  Every wait is bounded.
+//
+// Counting is batched: a courier adds what it has copied to the panel's counters when it moves on to another
+// (panel, publishing or not) group of jobs, or runs out of work -- one fence per group instead of one per 8 KB.
+// (A system-scope fence per batch limited the copy to ~130 GB/s.)  The publishing job of a panel comes first in
+// the list, so a courier always hands in its published batches BEFORE it starts waiting on another GPU's flag.
+__device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmParams& p, uint32_t lane, uint32_t panel,
+                                            uint32_t publish, uint32_t count) {
+    if (count == 0) return;
+    // the stores of every lane are performed before the counts below can be seen to include these batches:
+    // readers of pub_flags are other GPUs (system scope), readers of ready_flags are this GPU's loaders
+    if (publish) __threadfence_system(); else __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+        if (publish && atomicAdd(f.published + panel, count) + count == f.pub_need[panel]) {
+            __threadfence_system();
+            st_release_sys(f.pub_flags + panel, f.epoch);
+        }
+        if (atomicAdd(f.arrived + panel, count) + count == f.need[panel]) {
+            __threadfence();
+            st_release_sys(f.ready_flags + panel, f.epoch);
+            if (p.stats != nullptr) p.stats[panel] = global_timer_ns();
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParams& p, uint32_t courier,
                                            uint32_t n_couriers, uint32_t lane) {
     uint32_t job = 0, job_first = 0;             // first batch index of `job`
     uint32_t spr = 0, nseg = 0, nb = 0;
     FetchJob J;
     bool have = false, gate_open = false;
+    uint32_t pend_panel = 0, pend_pub = 0, pend = 0;      // batches copied but not yet counted
     for (uint32_t b = courier; b < f.total_batches; b += n_couriers) {
         for (;;) {                               // the job that holds batch b (batches only move forward)
             if (!have) {
-                if (job >= f.n_jobs) return;     // inconsistent table: stop rather than read past it
+                if (job >= f.n_jobs) {           // inconsistent table: stop rather than read past it
+                    fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
+                    return;
+                }
                 J = f.jobs[job];
                 spr = (J.bytes + 511u) / 512u;
                 nseg = J.rows * spr;
@@ -351,6 +385,12 @@ __device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParam
             job_first += nb;
             ++job;
             have = false;
+        }
+        if (J.panel != pend_panel || J.publish != pend_pub) {
+            fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
+            pend_panel = J.panel;
+            pend_pub = J.publish;
+            pend = 0;
         }
         if (!gate_open) {
             // the piece is being produced elsewhere (another GPU's couriers or a copy engine): wait for its flag
@@ -365,6 +405,7 @@ __device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParam
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (lane == 0) report(p, KS_TIMEOUT_FETCH);
+                fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
                 return;
             }
             (void)ld_acquire_sys(J.gate);        // every lane orders its own loads of the piece after the flag
@@ -385,20 +426,9 @@ __device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParam
 #pragma unroll
         for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
             if (off[u] != ~0ull) *reinterpret_cast<uint4*>(f.dst + off[u]) = v[u];
-        // the stores of every lane are performed before the counts below can be seen to include this batch
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-            if (atomicAdd(f.arrived + J.panel, 1u) + 1u == f.need[J.panel]) {
-                __threadfence_system();
-                st_release_sys(f.ready_flags + J.panel, f.epoch);
-            }
-            if (J.publish && atomicAdd(f.published + J.panel, 1u) + 1u == f.pub_need[J.panel]) {
-                __threadfence_system();
-                st_release_sys(f.pub_flags + J.panel, f.epoch);
-            }
-        }
+        ++pend;
     }
+    fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
 }
 
 template <int KIND, int CTAS, int NACC, int FETCH>
@@ -436,6 +466,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const uint32_t n_chunks = (n_kb + chunk_kb - 1) / chunk_kb;
 
     if (threadIdx.x == 0) {
+        if (p.stats != nullptr && blockIdx.x == 0) p.stats[16] = global_timer_ns();
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
@@ -480,9 +511,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     // B's panel may still be on its way: wait for its arrival flag, then make the data it
                     // guards visible to the TMA loads
                     const uint64_t t0 = global_timer_ns();
-                    bool arrived = true;
+                    bool arrived = true, waited = false;
                     while (int(ld_acquire_sys(p.panel_flags + panel) - p.panel_epoch) < 0) {
+                        waited = true;
                         if (global_timer_ns() - t0 > limit) { arrived = false; break; }
+                    }
+                    if (waited && p.stats != nullptr) {
+                        atomicAdd(p.stats + 18, (unsigned long long)(global_timer_ns() - t0));
+                        atomicAdd(p.stats + 19, 1ull);
                     }
                     if (!arrived) {
                         report(p, KS_TIMEOUT_PANEL);
@@ -775,6 +811,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
     }
     if constexpr (CTAS == 2) cluster_sync_all();
+    if (threadIdx.x == 0 && p.stats != nullptr) atomicMax(p.stats + 17, (unsigned long long)global_timer_ns());
 }
 
 }  // namespace dxb

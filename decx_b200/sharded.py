@@ -31,6 +31,14 @@ walks its tiles panel by panel and its loader waits on a panel's flag before tou
 (decxb200_gemm_fp16_panels).  No per-panel launches, so no round of the persistent grid is left half empty
 at a panel boundary, and the 256 x 512 tile applies.
 
+"fused" overlap (the default for fp16 on GPUs) goes one step further and needs no copy engine, no communication
+stream and no NCCL call inside the step: the GEMM kernel itself brings B in (decxb200_gemm_fp16_fetch).  Every
+CTA carries two courier warps; together they copy this rank's row piece of each panel from the owner's B
+(scatter: the owner sends every byte once), publish it through a flag in symmetric memory, and copy the other
+pieces from the ranks that hold them (all-gather), panel by panel, with 16-byte peer loads.  The tiles of a panel
+start when its pieces are counted complete.  One launch per rank does broadcast, product and -- through D in
+the owner's memory -- the gather; two stream-ordered symmetric-memory barriers bracket it.
+
 Rows are dealt in multiples of 256 (the CTA-pair tile height), so every rank runs whole tiles.
 """
 import ctypes
@@ -93,6 +101,58 @@ def panel_plan(N, panels, align=COL_ALIGN):
     return out
 
 
+def fetch_panel_plan(N, tile=512, max_panels=16):
+    """Column panels for the fused kernel: narrow ones first (two tiles = 1024 columns) so that the first
+    tiles start after a few dozen microseconds of transfer, four-tile panels afterwards (wider panels keep
+    the tiles that run together on fewer rows of A)."""
+    tiles = (N + tile - 1) // tile
+    widths, left = [], tiles
+    while left > 0:
+        w = 2 if len(widths) < 4 else 4
+        w = min(w, left)
+        widths.append(w)
+        left -= w
+    while len(widths) > max_panels:                 # very wide B: merge the last panels pairwise
+        widths[-2:] = [widths[-2] + widths[-1]]
+    return panel_plan(N, [w * tile for w in widths])
+
+
+def row_pieces(K, parts, align=16):
+    """[(first_row, rows)]: K rows of B cut into `parts` near-equal pieces (multiples of `align` rows)."""
+    units = (K + align - 1) // align
+    base, extra = divmod(units, parts)
+    out, r = [], 0
+    for i in range(parts):
+        n = min((base + (1 if i < extra else 0)) * align, K - r)
+        out.append((r, n))
+        r += n
+    return out
+
+
+def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr):
+    """Job list of `rank` for the fused kernel, as tuples (src, gate, row0, rows, col0, cols, panel, publish).
+
+    `active` are the ranks that run a kernel (they have rows of A); the non-owners among them each take one row
+    piece of every panel from the owner (published to the others) and the remaining pieces from each other.
+    b_ptr[r] / pub_ptr[r]: address of rank r's replica of B / of its publish flags, as this rank maps them."""
+    holders = [r for r in active if r != owner]
+    if rank == owner or rank not in holders:
+        return []
+    me = holders.index(rank)
+    pieces = row_pieces(K, len(holders))
+    jobs = []
+    for p, (c0, w) in enumerate(panels):
+        r0, nr = pieces[me]
+        if nr:
+            jobs.append((b_ptr[owner], None, r0, nr, c0, w, p, 1 if len(holders) > 1 else 0))
+        for d in range(1, len(holders)):
+            h = (me + d) % len(holders)                       # stagger the sources over the ranks
+            r0, nr = pieces[h]
+            if nr:
+                jobs.append((b_ptr[holders[h]], pub_ptr[holders[h]] + 4 * p, r0, nr, c0, w, p, 0))
+    return jobs
+
+
 class _RawCuda:
     """Lets torch view memory that was allocated through the C ABI (``__cuda_array_interface__``)."""
 
@@ -112,7 +172,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None, overlap=None):
+                 reserve_sms=None, bcast=None, overlap=None, tile=0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -140,14 +200,20 @@ class ShardedGemm:
         self.overlap = "panels"                 # one GEMM launch per panel
         if self.world > 1 and self.bcast == "p2p" and (not self.on_gpu or K % self.world != 0):
             self.bcast = "broadcast"
-        if (overlap in (None, "single") and self.world > 1 and self.bcast == "p2p" and dtype == torch.float16
-                and gemm_fn is None and self.gather == "peer" and N % 8 == 0):
+        if (overlap in (None, "fused") and self.world > 1 and self.on_gpu and dtype == torch.float16
+                and gemm_fn is None and self.gather == "peer" and N % 8 == 0 and bcast in (None, "p2p")):
+            self.panels = fetch_panel_plan(N) if panels == "ramp" else panel_plan(N, panels, align=512)
+            if len(self.panels) <= 16 and self._setup_fused():
+                self.overlap = "fused"
+                self.bcast = "in-kernel"
+        if (self.overlap != "fused" and overlap in (None, "single") and self.world > 1 and self.bcast == "p2p"
+                and dtype == torch.float16 and gemm_fn is None and self.gather == "peer" and N % 8 == 0):
             self.panels = panel_plan(N, panels, align=512)
             if len(self.panels) <= 8 and self._setup_symmetric_replica():
                 self.overlap = "single"
-        if self.world > 1 and self.bcast == "p2p" and self.overlap != "single":
+        if self.world > 1 and self.bcast == "p2p" and self.overlap not in ("single", "fused"):
             self._setup_symmetric_panels()
-        if self.overlap == "single":
+        if self.overlap in ("single", "fused"):
             self.Bp = None
         elif self.world > 1 and self._hdl is None:
             self.Bp = [torch.empty((K, w), dtype=dtype, device=dev) for _, w in self.panels]
@@ -174,6 +240,10 @@ class ShardedGemm:
             self._max_ctas = max(2, sms - self.reserve_sms) if self.reserve_sms else 0
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.events = [torch.cuda.Event() for _ in self.panels]
+            self._tile = tile
+            self.kernel_variant = 0
+            if self.overlap == "fused":
+                self._fused_prepare()
         if self.gather == "peer":
             self._setup_peer_d()
         else:
@@ -227,6 +297,69 @@ class ShardedGemm:
             self.bcast = "broadcast"
             return False
 
+    # ------------------------------------------------------------------ "fused": the kernel fetches B itself
+    def _setup_fused(self):
+        """A full K x N replica of B per rank plus two flag arrays in ONE symmetric allocation (the owner's
+        replica is its B); every rank maps every other rank's copy."""
+        import sys
+        try:
+            import torch.distributed._symmetric_memory as symm
+            n = self.K * self.N
+            self._bsym = symm.empty(n + 128, dtype=self.dtype, device=self.device)     # + 256 bytes of flags
+            grp = self.group if self.group is not None else dist.group.WORLD
+            self._hdl = symm.rendezvous(self._bsym, group=grp)
+            self._bptrs = [int(p) for p in self._hdl.buffer_ptrs]
+            self.Bfull = self._bsym[:n].view(self.K, self.N)
+            if self.is_owner:
+                self.B = self.Bfull
+            words = self._bsym[n:].view(torch.int32)
+            words.zero_()
+            self.flags, self.pub_flags = words[:16], words[16:32]
+            self._pub_ptrs = [p + n * self._esz_of(self.dtype) + 64 for p in self._bptrs]
+            return True
+        except Exception as e:
+            print(f"decx_b200.sharded: symmetric memory unavailable ({type(e).__name__}: {e}); copy-engine delivery",
+                  file=sys.stderr)
+            self._hdl = None
+            return False
+
+    @staticmethod
+    def _esz_of(dtype):
+        return torch.empty(0, dtype=dtype).element_size()
+
+    def _fused_prepare(self):
+        capi = self._capi
+        active = [r for r, (_, n) in enumerate(self.rows) if n > 0]
+        tuples = fetch_jobs(self.rank, self.owner, active, self.K, self.panels, self._bptrs, self._pub_ptrs)
+        self._jobs = [capi.FetchJob(*t) for t in tuples]
+        need = int(capi.lib.decxb200_fetch_scratch_bytes(max(len(self._jobs), 1)))
+        self._fetch_scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
+
+    def _fused_gemm(self, epoch, fetch=True):
+        if self.nrows == 0:
+            return
+        G = self._G
+        ends = [c0 + w for c0, w in self.panels]
+        jobs = self._jobs if fetch else []
+        gated = bool(jobs) or not self.is_owner
+        with torch.cuda.device(self.device):
+            G.gemm_fp16_fetch(self.A, self.Bfull, self._d_ptr, self.N, ends, self.flags if gated else None,
+                              self.pub_flags if jobs else None, epoch, jobs, self._fetch_scratch if jobs else None,
+                              status=self.status, max_ctas=self._max_ctas, tile=self._tile)
+        self.launches += self._capi.lib.decxb200_last_launch_count()
+        self.kernel_variant = self._capi.lib.decxb200_last_kernel_variant()
+
+    def fetch_stats(self):
+        """Timing record of the last fused launch on this rank (after a synchronize), in microseconds relative
+        to the kernel's start: when each panel was complete, kernel duration, total loader wait."""
+        if self.overlap != "fused" or not self._jobs:
+            return None
+        w = self._fetch_scratch[256:512].view(torch.int64).cpu().tolist()
+        t0 = w[16]
+        return {"panel_ready_us": [round((w[i] - t0) / 1e3, 1) for i in range(len(self.panels))],
+                "kernel_us": round((w[17] - t0) / 1e3, 1), "loader_wait_us_sum": round(w[18] / 1e3, 1),
+                "loader_waits": w[19]}
+
     def _deliver_replica(self, epoch):
         """Communication stream of the "single" overlap: fill this rank's replica of B panel by panel and flag
         each panel.  Every rank pulls its row block of the panel from the owner, then the other row blocks from
@@ -273,13 +406,16 @@ class ShardedGemm:
         capi.check(capi.lib.decxb200_gemm_fp16_panels(
             torch.cuda.current_stream(self.device).cuda_stream, self.nrows, self.N, self.K,
             self.A.data_ptr(), self.A.stride(0), self.Bfull.data_ptr(), self.N, self._d_ptr, self.N,
-            self.status.data_ptr(), len(ends), arr, self.flags.data_ptr(), epoch, self._max_ctas, 0))
+            self.status.data_ptr(), len(ends), arr, self.flags.data_ptr(), epoch, self._max_ctas, self._tile))
         self.launches += capi.lib.decxb200_last_launch_count()
+        self.kernel_variant = capi.lib.decxb200_last_kernel_variant()
 
     def compute_only(self):
         """This rank's GEMM launch(es) with B already in place and no communication (for kernel timing)."""
         self.launches = 0
-        if self.overlap == "single":
+        if self.overlap == "fused":
+            self._fused_gemm(self._epoch, fetch=False)     # the replica and its flags hold this epoch
+        elif self.overlap == "single":
             self._single_gemm(self._epoch)                 # the flags already hold this epoch
         else:
             for j in range(len(self.panels)):
@@ -390,6 +526,13 @@ class ShardedGemm:
         if self.world == 1:
             self.Bp = [self.B]
             self._panel_gemm(0)
+            return
+        if self.overlap == "fused":
+            with torch.cuda.device(self.device):
+                self._epoch += 1
+                self._hdl.barrier(channel=0)               # B is final on the owner; nobody still reads the old replicas
+                self._fused_gemm(self._epoch)
+                self._hdl.barrier(channel=1)               # every rank's rows have reached the owner
             return
         if self.overlap == "single":
             with torch.cuda.device(self.device):

@@ -189,7 +189,10 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
  *   jobs:      HOST array, copied by the call.  gate == NULL: the source is readable now.  rows == 0: a piece
  *              that something else writes into the replica (a copy engine); the courier only waits for its
  *              gate and counts it.  Every panel needs at least one job.  col0, cols: multiples of 8.
- *   scratch:   device memory, 256-byte aligned, decxb200_fetch_scratch_bytes(n_jobs) bytes (counters + job table).
+ *   scratch:   device memory, 256-byte aligned, decxb200_fetch_scratch_bytes(n_jobs) bytes (counters, a timing
+ *              record, the job table).  After the kernel, bytes [256, 512) hold 32 uint64 in ns of the GPU's
+ *              global timer: [i] when panel i was complete, [16] kernel start, [17] kernel end, [18] total time
+ *              the tile loaders waited for panels, [19] how many such waits.
  *   ready_flags, pub_flags: device words, one per panel; other GPUs must be able to read pub_flags.
  *   n_jobs == 0: this GPU already holds B (the owner); ready_flags may then be NULL (no gating at all).
  *   All waits are bounded: status 0x106 (a panel never completed) or 0x107 (a gate never opened).

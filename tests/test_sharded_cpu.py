@@ -93,3 +93,49 @@ def test_two_rank_schedule_over_gloo(shape, bcast):
         p.join(120)
         assert p.exitcode == 0
     assert q.get(timeout=5) is True
+
+
+# ------------------------------------------------------------------ planning of the fused (in-kernel fetch) path
+def test_fetch_panel_plan_and_row_pieces():
+    from decx_b200.sharded import fetch_panel_plan, row_pieces
+    for N in (8, 520, 1024, 2104, 16384, 40000):
+        plan = fetch_panel_plan(N)
+        assert len(plan) <= 16 and plan[0][0] == 0 and sum(w for _, w in plan) == N
+        assert all(c % 512 == 0 for c, _ in plan)                          # panels start on 256 x 512 tile columns
+        assert all(a[0] + a[1] == b[0] for a, b in zip(plan, plan[1:]))
+    for K, parts in ((16384, 7), (2053, 3), (70, 1), (16, 4), (130, 7)):
+        pc = row_pieces(K, parts)
+        assert len(pc) == parts and pc[0][0] == 0 and sum(n for _, n in pc) == K
+        assert all(a[0] + a[1] == b[0] for a, b in zip(pc, pc[1:]))
+
+
+def test_fetch_jobs_cover_b_exactly_once_and_gate_on_the_publisher():
+    from decx_b200.sharded import fetch_jobs, fetch_panel_plan, row_pieces
+    K, N = 2053, 2104
+    panels = fetch_panel_plan(N)
+    for world, owner, active in ((2, 0, [0, 1]), (4, 0, [0, 1, 2, 3]), (8, 3, list(range(8))), (4, 0, [0, 1, 2])):
+        b_ptr = [1000 * (r + 1) for r in range(world)]
+        pub_ptr = [50 + 1000 * (r + 1) for r in range(world)]
+        published = {}                                                     # (rank, panel) -> rows it publishes
+        for r in range(world):
+            jobs = fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr)
+            if r == owner or r not in active:
+                assert jobs == []
+                continue
+            for p, (c0, w) in enumerate(panels):
+                mine = [j for j in jobs if j[6] == p]
+                assert all(j[4] == c0 and j[5] == w for j in mine)
+                rows = sorted((j[2], j[3]) for j in mine)
+                assert rows[0][0] == 0 and sum(n for _, n in rows) == K    # every row of the panel, once
+                assert all(a[0] + a[1] == b[0] for a, b in zip(rows, rows[1:]))
+                own = [j for j in mine if j[0] == b_ptr[owner]]
+                assert len(own) == 1 and own[0][1] is None                 # one piece straight from the owner
+                published[(r, p)] = (own[0][2], own[0][3])
+                assert mine[0] is own[0] or mine[0] == own[0]              # and it comes first (others wait on it)
+        # a gated job reads exactly the rows its source publishes, behind that source's flag for the panel
+        for r in range(world):
+            for j in fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr):
+                if j[1] is not None:
+                    src_rank = b_ptr.index(j[0])
+                    assert j[1] == pub_ptr[src_rank] + 4 * j[6] and j[7] == 0
+                    assert published[(src_rank, j[6])] == (j[2], j[3])
