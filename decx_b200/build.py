@@ -35,7 +35,7 @@ def build_kernels(force=False, verbose=False):
     srcs.append(os.path.join(ROOT, "include", "decx_b200.h"))
     if force or _stale(out, srcs):
         cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
-            "-shared", "-o", out, os.path.join(CSRC, "capi.cu")]
+            "-shared", "-o", out] + [f for f in srcs if f.endswith(".cu")]
         subprocess.run(cmd, check=True, cwd=CSRC)
     return out
 

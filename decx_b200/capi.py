@@ -7,7 +7,9 @@ fails the error code is turned into ``DecxB200Error``.
 import ctypes
 import os
 
-FP32, FP16, CPLXF = 1, 3, 5
+FP32, FP64, FP16, CPLXF, CPLXD = 1, 2, 3, 5, 6
+ACCU_L1, ACCU_L2, ACCU_L3 = 0, 1, 2
+CAST_F32_F16, CAST_F16_F32, CAST_F32_F64, CAST_F64_F32, CAST_I32_F32, CAST_F32_I32 = range(6)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "libdecx_b200.so")
@@ -54,6 +56,14 @@ def _load():
     lib.decxb200_gemm_fp16_fetch.restype = ci
     lib.decxb200_gemm_fp16_fetch.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32, ctypes.POINTER(u32),
                                              vp, vp, ctypes.c_uint, ctypes.POINTER(FetchJob), u32, vp, sz, ci, ci]
+    lib.decxb200_gemv_workspace_bytes.restype = sz
+    lib.decxb200_gemv_workspace_bytes.argtypes = [ci, ci, ci, u32, u32]
+    lib.decxb200_gemv.restype = ci
+    lib.decxb200_gemv.argtypes = [ci, ci, ci, vp, u32, u32, vp, u64, vp, vp, vp, sz]
+    lib.decxb200_transpose.restype = ci
+    lib.decxb200_transpose.argtypes = [ci, vp, u32, u32, vp, u64, vp, u64]
+    lib.decxb200_cast2d.restype = ci
+    lib.decxb200_cast2d.argtypes = [ci, vp, u32, u32, vp, u64, vp, u64]
     lib.decxb200_copy2d_async.restype = ci
     lib.decxb200_copy2d_async.argtypes = [vp, vp, sz, vp, sz, sz, sz]
     lib.decxb200_write_flag_async.restype = ci
@@ -85,7 +95,8 @@ lib = _load()
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
-    "decxb200_gemm_fp32_noalloc",
+    "decxb200_gemm_fp32_noalloc", "decxb200_gemv_workspace_bytes", "decxb200_gemv", "decxb200_transpose",
+    "decxb200_cast2d",
     "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_strerror", "decxb200_version",

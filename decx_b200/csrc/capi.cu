@@ -6,12 +6,22 @@
 #include <vector>
 
 #include "../../include/decx_b200.h"
+#include "capi_shared.h"
 #include "gemm_sm100.cuh"
 #include "prepass.cuh"
+
+namespace dxb_host {
+thread_local int t_launches = 0;
+void count_launch(int n) { t_launches += n; }
+void reset_launches() { t_launches = 0; }
+}  // namespace dxb_host
+using dxb_host::t_launches;
 
 namespace {
 
 using namespace dxb;
+using dxb_host::round_up;
+using dxb_host::aligned16;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -41,10 +51,8 @@ struct DeviceInfo {
 DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
 
-thread_local int t_launches = 0;
 thread_local int t_variant = 0;    // KIND*100 + CTAS*10 + NACC of the last GEMM kernel this thread launched
 
-inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
 // 2-D row-major tensor (rows x cols, `ld` elements per row) with a (box_cols x box_rows) box,
 // 128-byte swizzle (of 16-byte units unless `swizzle` says otherwise), zero fill outside [0, cols) x [0, rows).
@@ -199,6 +207,7 @@ size_t decxb200_gemm_workspace_bytes(int dtype, uint32_t M, uint32_t N, uint32_t
         const uint64_t b = round_up(2ull * K * round_up(2ull * N, 32) * 4, 256);
         return size_t(2 * a + 2 * b);
     }
+    if (dtype == DECXB200_CPLXD) return dxb_host::f64_workspace_bytes(true, M, N, K);
     return 0;
 }
 
@@ -226,7 +235,6 @@ Scalars read_scalars(int dtype, const void* alpha, const void* beta) {
     return s;
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline unsigned prepass_blocks(uint64_t work) {
     const uint64_t b = work / 256 + 1;
@@ -397,14 +405,17 @@ int run_tf32(cudaStream_t stream, int dev, bool cplx, uint32_t M, uint32_t N, ui
 
 int check_common(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, const void* B,
                  uint64_t ldb, const void* C, uint64_t ldc, const void* D, uint64_t ldd, int& cta_group, int& dev) {
-    if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF) return DECXB200_EINVAL;
+    if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF && dtype != DECXB200_FP64 &&
+        dtype != DECXB200_CPLXD)
+        return DECXB200_EINVAL;
     if (A == nullptr || B == nullptr || D == nullptr) return DECXB200_EINVAL;
     if (M == 0 || N == 0 || K == 0) return DECXB200_EINVAL;
     if (lda < K || ldb < N || ldd < N || (C != nullptr && ldc < N)) return DECXB200_EINVAL;
     if (cta_group == 0) cta_group = default_cta_group();
     if (cta_group != 1 && cta_group != 2 && !(cta_group == DECXB200_TILE_256x512 && dtype == DECXB200_FP16))
         return DECXB200_EINVAL;
-    if (dtype == DECXB200_CPLXF && (uint64_t(N) * 2 > 0xFFFFFFFFull || uint64_t(K) * 2 > 0xFFFFFFFFull))
+    if ((dtype == DECXB200_CPLXF || dtype == DECXB200_CPLXD) &&
+        (uint64_t(N) * 2 > 0xFFFFFFFFull || uint64_t(K) * 2 > 0xFFFFFFFFull))
         return DECXB200_ETOOLARGE;
     const cudaError_t ce = cudaGetDevice(&dev);
     if (ce != cudaSuccess) return int(ce);
@@ -412,7 +423,27 @@ int check_common(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, u
     return 0;
 }
 
-inline uint64_t elem_size(int dtype) { return dtype == DECXB200_FP16 ? 2 : (dtype == DECXB200_FP32 ? 4 : 8); }
+inline uint64_t elem_size(int dtype) {
+    switch (dtype) {
+        case DECXB200_FP16: return 2;
+        case DECXB200_FP32: return 4;
+        case DECXB200_CPLXD: return 16;
+        default: return 8;                       // fp64, complex fp32
+    }
+}
+inline bool is_f64(int dtype) { return dtype == DECXB200_FP64 || dtype == DECXB200_CPLXD; }
+// alpha / beta of the 64-bit types: host pointers to double (double[2] for complex); NULL = 1 / 0
+inline void read_scalars_f64(int dtype, const void* alpha, const void* beta, double a[2], double b[2]) {
+    a[0] = 1.0; a[1] = 0.0; b[0] = 0.0; b[1] = 0.0;
+    if (alpha != nullptr) {
+        a[0] = static_cast<const double*>(alpha)[0];
+        if (dtype == DECXB200_CPLXD) a[1] = static_cast<const double*>(alpha)[1];
+    }
+    if (beta != nullptr) {
+        b[0] = static_cast<const double*>(beta)[0];
+        if (dtype == DECXB200_CPLXD) b[1] = static_cast<const double*>(beta)[1];
+    }
+}
 // device row pitch (elements) of the staging copies: the reference's rule for device matrices, rows
 // rounded up to 128 bytes (srcs/modules/core/classes/GPU_Matrix.cu:35-61)
 inline uint64_t dev_pitch(int dtype, uint64_t width) { return round_up(width * elem_size(dtype), 128) / elem_size(dtype); }
@@ -460,7 +491,7 @@ HostArena plan_arena(int dtype, uint32_t M, uint32_t N, uint32_t K, bool has_c) 
     HostArena a;
     memset(&a, 0, sizeof(a));
     const uint64_t es = elem_size(dtype);
-    const bool cplx = dtype == DECXB200_CPLXF, split = dtype != DECXB200_FP16;
+    const bool cplx = dtype == DECXB200_CPLXF, split = (dtype == DECXB200_FP32 || dtype == DECXB200_CPLXF);
     a.rb = host_block_rows(M);
     a.ldb_d = dev_pitch(dtype, N);
     a.lda_d = dev_pitch(dtype, K);
@@ -474,6 +505,8 @@ HostArena plan_arena(int dtype, uint32_t M, uint32_t N, uint32_t K, bool has_c) 
         const uint64_t kb = (cplx ? 2ull * K : K) * a.ldbw * 4;
         a.b_hi = take(kb);
         a.b_lo = take(kb);
+    } else if (dtype == DECXB200_CPLXD) {
+        a.b_hi = take(dxb_host::f64_workspace_bytes(true, M, N, K));    // real expansion of B
     }
     for (int i = 0; i < 2; ++i) {
         a.a_dev[i] = take(uint64_t(a.rb) * a.lda_d * es);
@@ -501,6 +534,13 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
     int rc = check_common(dtype, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, cta_group, dev);
     if (rc != 0) return rc;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (is_f64(dtype)) {
+        // no tcgen05 kind for fp64: warp-level DMMA kernel (gemm_f64.cuh); the tile knobs do not apply
+        double a[2], b[2];
+        read_scalars_f64(dtype, alpha, beta, a, b);
+        return dxb_host::run_f64(stream, dtype == DECXB200_CPLXD, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, a, b,
+                                 workspace, workspace_bytes);
+    }
     const Scalars sc = read_scalars(dtype, alpha, beta);
     if (dtype == DECXB200_FP16)
         return run_f16(stream, dev, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, sc, status, cta_group, max_ctas);
@@ -527,7 +567,7 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
 
 size_t decxb200_gemm_host_arena_bytes(int dtype, uint32_t M, uint32_t N, uint32_t K, int has_c) {
     if (M == 0 || N == 0 || K == 0) return 0;
-    if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF) return 0;
+    if (dtype != DECXB200_FP32 && dtype != DECXB200_FP16 && dtype != DECXB200_CPLXF && !is_f64(dtype)) return 0;
     return size_t(plan_arena(dtype, M, N, K, has_c != 0).total);
 }
 
@@ -538,7 +578,14 @@ int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
     int dev = 0, cta_group = 0;
     int rc = check_common(dtype, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, cta_group, dev);
     if (rc != 0) return rc;
-    const Scalars sc = read_scalars(dtype, alpha, beta);
+    Scalars sc;
+    double a64[2] = {1.0, 0.0}, b64[2] = {0.0, 0.0};
+    if (is_f64(dtype)) {
+        read_scalars_f64(dtype, alpha, beta, a64, b64);
+        sc.br = (b64[0] != 0.0 || b64[1] != 0.0) ? 1.f : 0.f;          // only "is C used" is read from sc below
+    } else {
+        sc = read_scalars(dtype, alpha, beta);
+    }
     const bool use_c = (C != nullptr) && (sc.br != 0.f || sc.bi != 0.f);
     const HostArena ar = plan_arena(dtype, M, N, K, use_c);
     if (arena == nullptr || arena_bytes < ar.total || (reinterpret_cast<uintptr_t>(arena) & 255) != 0)
@@ -547,7 +594,7 @@ int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
     if ((rc = host_path(dev, hp)) != 0) return rc;
 
     const uint64_t es = elem_size(dtype);
-    const bool cplx = dtype == DECXB200_CPLXF, split = dtype != DECXB200_FP16;
+    const bool cplx = dtype == DECXB200_CPLXF, split = (dtype == DECXB200_FP32 || dtype == DECXB200_CPLXF);
     uint8_t* base = static_cast<uint8_t*>(arena);
     auto at = [&](uint64_t off) { return base + off; };
     cudaError_t e;
@@ -581,7 +628,12 @@ int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
         DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_h2d[b], 0));
         if (step >= 2) DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_d2h[b], 0));  // D staging buffer drained
         const void* c_dev = use_c ? at(ar.c_dev[b]) : nullptr;
-        if (!split) {
+        if (is_f64(dtype)) {
+            const size_t wsb = dxb_host::f64_workspace_bytes(dtype == DECXB200_CPLXD, M, N, K);
+            rc = dxb_host::run_f64(hp->comp, dtype == DECXB200_CPLXD, rows, N, K, at(ar.a_dev[b]), ar.lda_d,
+                                   at(ar.b_dev), ar.ldb_d, c_dev, ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, a64, b64,
+                                   wsb ? at(ar.b_hi) : nullptr, wsb, step > 0);
+        } else if (!split) {
             rc = run_f16(hp->comp, dev, rows, N, K, at(ar.a_dev[b]), ar.lda_d, at(ar.b_dev), ar.ldb_d, c_dev,
                          ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, sc, status, cta_group, 0);
         } else {

@@ -1,0 +1,23 @@
+// Small internals shared by the translation units of libdecx_b200.so.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace dxb_host {
+
+// per-thread count of kernels launched by the current C-ABI call (decxb200_last_launch_count)
+void count_launch(int n = 1);
+void reset_launches();
+
+inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// fp64 / complex-fp64 GEMM on `stream` (real expansion of B in `workspace` for the complex case;
+// b_expanded: the workspace already holds it, e.g. from the previous row block of the same B)
+int run_f64(cudaStream_t stream, bool cplx, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
+            const void* B, uint64_t ldb, const void* C, uint64_t ldc, void* D, uint64_t ldd, const double alpha[2],
+            const double beta[2], void* workspace, size_t workspace_bytes, bool b_expanded = false);
+size_t f64_workspace_bytes(bool cplx, uint32_t M, uint32_t N, uint32_t K);
+
+}  // namespace dxb_host

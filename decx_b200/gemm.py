@@ -12,7 +12,8 @@ import torch
 
 from . import capi
 
-_DTYPES = {torch.float32: capi.FP32, torch.float16: capi.FP16, torch.complex64: capi.CPLXF}
+_DTYPES = {torch.float32: capi.FP32, torch.float16: capi.FP16, torch.complex64: capi.CPLXF,
+           torch.float64: capi.FP64, torch.complex128: capi.CPLXD}
 
 
 def _ld(t):
@@ -27,6 +28,11 @@ def _scalar(dtype, v):
     if dtype == capi.CPLXF:
         c = complex(v)
         buf = (ctypes.c_float * 2)(c.real, c.imag)
+    elif dtype == capi.CPLXD:
+        c = complex(v)
+        buf = (ctypes.c_double * 2)(c.real, c.imag)
+    elif dtype == capi.FP64:
+        buf = (ctypes.c_double * 1)(float(v))
     else:
         buf = (ctypes.c_float * 1)(float(v))
     return buf, ctypes.cast(buf, ctypes.c_void_p)
@@ -42,7 +48,7 @@ def gemm(A, B, C=None, alpha=None, beta=None, out=None, workspace=None, status=N
         raise RuntimeError("decx_b200.gemm works on CUDA tensors only (no CPU fallback)")
     dt = _DTYPES.get(A.dtype)
     if dt is None or B.dtype != A.dtype or (C is not None and C.dtype != A.dtype):
-        raise TypeError("A, B, C must share one dtype out of float16, float32, complex64")
+        raise TypeError("A, B, C must share one dtype out of float16, float32, float64, complex64, complex128")
     M, K = A.shape
     K2, N = B.shape
     if K2 != K:
@@ -85,7 +91,7 @@ def gemm_host(A, B, C=None, alpha=None, beta=None, out=None, arena=None, status=
         raise RuntimeError("decx_b200 needs a CUDA device (no CPU fallback)")
     dt = _DTYPES.get(A.dtype)
     if dt is None or B.dtype != A.dtype or (C is not None and C.dtype != A.dtype):
-        raise TypeError("A, B, C must share one dtype out of float16, float32, complex64")
+        raise TypeError("A, B, C must share one dtype out of float16, float32, float64, complex64, complex128")
     M, K = A.shape
     K2, N = B.shape
     if K2 != K:

@@ -112,13 +112,35 @@ std::condition_variable g_res_cv;
 std::thread g_res_thread;
 bool g_res_stop = false, g_res_started = false;
 
+struct GenericResource {       // one ResourceCheckIn registration; ids are indices and are never reused
+    void** exposed = nullptr;
+    double lifespan = 0.0, last_used = 0.0;
+    decx::res_release_fn release = nullptr;
+    bool occupied = false, alive = false;
+};
+std::vector<GenericResource> g_generic;
+
 void manager_loop() {
     std::unique_lock<std::mutex> lk(g_res_mtx);
     while (!g_res_stop) {
-        g_res_cv.wait_for(lk, std::chrono::milliseconds(500));
+        g_res_cv.wait_for(lk, std::chrono::milliseconds(200));
         if (g_res_stop) break;
         const double now = decx::res::now_seconds();
         for (decx::ScratchResource* r : g_resources) r->collect_if_idle(now);
+        for (GenericResource& g : g_generic) {
+            if (!g.alive || g.occupied || g.exposed == nullptr || *g.exposed == nullptr) continue;
+            if (now - g.last_used > g.lifespan) {
+                if (g.release != nullptr) g.release(*g.exposed);
+                *g.exposed = nullptr;
+            }
+        }
+    }
+}
+
+void start_manager_locked() {
+    if (!g_res_started) {
+        g_res_started = true;
+        g_res_thread = std::thread(manager_loop);
     }
 }
 
@@ -141,10 +163,44 @@ double decx::res::now_seconds() {
 void decx::res::register_resource(decx::ScratchResource* r) {
     std::lock_guard<std::mutex> lk(g_res_mtx);
     g_resources.push_back(r);
-    if (!g_res_started) {
-        g_res_started = true;
-        g_res_thread = std::thread(manager_loop);
+    start_manager_locked();
+}
+
+uint64_t decx::ResourceCheckIn(void** exposed_ptr, const time_t lifespan_sec, decx::res_release_fn _decon) {
+    std::lock_guard<std::mutex> lk(g_res_mtx);
+    GenericResource g;
+    g.exposed = exposed_ptr;
+    g.lifespan = double(lifespan_sec);
+    g.last_used = decx::res::now_seconds();
+    g.release = _decon;
+    g.alive = true;
+    g_generic.push_back(g);
+    start_manager_locked();
+    return g_generic.size() - 1;
+}
+
+void decx::ResourceLock(const uint64_t res_id) {
+    std::lock_guard<std::mutex> lk(g_res_mtx);
+    if (res_id < g_generic.size()) g_generic[res_id].occupied = true;
+}
+
+void decx::ResourceUnlock(const uint64_t res_id) {
+    std::lock_guard<std::mutex> lk(g_res_mtx);
+    if (res_id < g_generic.size()) {
+        g_generic[res_id].occupied = false;
+        g_generic[res_id].last_used = decx::res::now_seconds();
     }
+}
+
+void decx::ResourceCheckOut(const uint64_t res_id) {
+    std::lock_guard<std::mutex> lk(g_res_mtx);
+    if (res_id >= g_generic.size() || !g_generic[res_id].alive) return;
+    GenericResource& g = g_generic[res_id];
+    if (g.exposed != nullptr && *g.exposed != nullptr) {
+        if (g.release != nullptr) g.release(*g.exposed);
+        *g.exposed = nullptr;
+    }
+    g.alive = false;
 }
 
 void decx::res::unregister_resource(decx::ScratchResource* r) {

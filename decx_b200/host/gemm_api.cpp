@@ -18,21 +18,30 @@ int abi_dtype(de::_DATA_TYPES_FLAGS_ t) {
         case de::_FP32_: return DECXB200_FP32;
         case de::_FP16_: return DECXB200_FP16;
         case de::_COMPLEX_F32_: return DECXB200_CPLXF;
+        case de::_FP64_: return DECXB200_FP64;
+        case de::_COMPLEX_F64_: return DECXB200_CPLXD;
         default: return -1;
     }
 }
 
 void fail(int code, const char* msg) { decx::err::set(de::GetLastError(), code, msg); }
 
-// alpha / beta as the accumulate type the C ABI wants (float, or {re, im})
-bool scalar_of(const de::Number& n, de::_DATA_TYPES_FLAGS_ t, float out[2]) {
+// alpha / beta as the accumulate type the C ABI wants: float / {re, im} floats for the 16/32-bit types, double /
+// {re, im} doubles for fp64 and complex fp64 (the same 16 bytes hold either)
+union AbiScalar {
+    float f[2];
+    double d[2];
+};
+bool scalar_of(const de::Number& n, de::_DATA_TYPES_FLAGS_ t, AbiScalar& out) {
     if (n.Type() != int32_t(t)) return false;
-    out[1] = 0.f;
-    if (t == de::_FP32_) out[0] = n.get_data_ref<float>();
-    else if (t == de::_FP16_) out[0] = de::Half2Float(n.get_data_ref<de::Half>());
+    if (t == de::_FP64_) { out.d[0] = n.get_data_ref<double>(); out.d[1] = 0.0; return true; }
+    if (t == de::_COMPLEX_F64_) { out.d[0] = n.get_data_ref<de::CPd>().real; out.d[1] = n.get_data_ref<de::CPd>().image; return true; }
+    out.f[1] = 0.f;
+    if (t == de::_FP32_) out.f[0] = n.get_data_ref<float>();
+    else if (t == de::_FP16_) out.f[0] = de::Half2Float(n.get_data_ref<de::Half>());
     else {
-        out[0] = n.get_data_ref<de::CPf>().real;
-        out[1] = n.get_data_ref<de::CPf>().image;
+        out.f[0] = n.get_data_ref<de::CPf>().real;
+        out.f[1] = n.get_data_ref<de::CPf>().image;
     }
     return true;
 }
@@ -115,7 +124,7 @@ void gemm_device(de::GPU_Matrix& A_, de::GPU_Matrix& B_, de::GPU_Matrix* C_, de:
     if (dt < 0) return fail(de::DECX_FAIL_UNSUPPORTED_TYPE, "error: The data type is not supported by GEMM on this path");
     if (C && (C->Width() != B->Width() || C->Height() != A->Height()))
         return fail(de::DECX_FAIL_DimsNotMatching, "error: Dim(s) is(are) not equal to each other");
-    float a[2] = {1.f, 0.f}, b[2] = {0.f, 0.f};
+    AbiScalar a, b;
     if (C) {
         if (!scalar_of(*alpha, A->Type(), a) || !scalar_of(*beta, A->Type(), b))
             return fail(de::DECX_FAIL_TYPE_MOT_MATCH, "error: The types of the two objects are not equal");
@@ -151,8 +160,8 @@ void gemm_device(de::GPU_Matrix& A_, de::GPU_Matrix& B_, de::GPU_Matrix* C_, de:
         }
     }
     const int rc = decxb200_gemm(dt, S->get_raw_stream_ref(), M, N, K, A->Mat.ptr, A->Pitch(), B->Mat.ptr, B->Pitch(),
-                                 C ? C->Mat.ptr : nullptr, C ? C->Pitch() : 0, dst->Mat.ptr, dst->Pitch(), C ? a : nullptr,
-                                 C ? b : nullptr, ws, need, static_cast<unsigned*>(sw->dev.ptr));
+                                 C ? C->Mat.ptr : nullptr, C ? C->Pitch() : 0, dst->Mat.ptr, dst->Pitch(), C ? &a : nullptr,
+                                 C ? &b : nullptr, ws, need, static_cast<unsigned*>(sw->dev.ptr));
     if (rc == 0)
         cudaMemcpyAsync(sw->host, sw->dev.ptr, sizeof(unsigned), cudaMemcpyDeviceToHost, S->get_raw_stream_ref());
     E->event_record(S);
@@ -198,9 +207,11 @@ void gemm_host(de::Matrix& A_, de::Matrix& B_, de::Matrix* C_, de::Matrix& dst_)
         if (arena != nullptr) arena_cache()->unlock();
         return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
     }
-    const float one[2] = {1.f, 0.f};
+    AbiScalar one;
+    if (A->Type() == de::_FP64_ || A->Type() == de::_COMPLEX_F64_) { one.d[0] = 1.0; one.d[1] = 0.0; }
+    else { one.f[0] = 1.f; one.f[1] = 0.f; }
     const int rc = decxb200_gemm_host(dt, M, N, K, A->data, A->Pitch(), B->data, B->Pitch(), C ? C->data : nullptr,
-                                      C ? C->Pitch() : 0, dst->data, dst->Pitch(), C ? one : nullptr, C ? one : nullptr,
+                                      C ? C->Pitch() : 0, dst->data, dst->Pitch(), C ? &one : nullptr, C ? &one : nullptr,
                                       arena, need, static_cast<unsigned*>(sw->dev.ptr));
     arena_cache()->unlock();
     if (rc == DECXB200_EKERNEL) {

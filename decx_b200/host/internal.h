@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <ctime>
 #include <mutex>
 #include <vector>
 
@@ -60,8 +61,23 @@ public:
 namespace cuda {
 _DECX_API_ decx::cuda_stream* get_cuda_stream_ptr(const int flag);   // nullptr on failure
 _DECX_API_ decx::cuda_event* get_cuda_event_ptr(const int flag);
+// reference forms of the two calls above (cudaStream_package.h:81-90, cudaEvent_package.h): the caller must
+// know that a stream / event can be had -- on failure these return a static, never-attached dummy whose raw
+// handle is null
+_DECX_API_ decx::cuda_stream& get_cuda_stream_ref(const int flag);
+_DECX_API_ decx::cuda_event& get_cuda_event_ref(const int flag);
 _DECX_API_ void release_stream_event_pools();
 _DECX_API_ size_t pooled_stream_count();
+_DECX_API_ size_t pooled_event_count();
+// test hook: replace stream / event creation and destruction and the "current device" query (nullptr = CUDA)
+struct RawHooks {
+    int (*stream_create)(cudaStream_t*, unsigned);
+    int (*stream_destroy)(cudaStream_t);
+    int (*event_create)(cudaEvent_t*, unsigned);
+    int (*event_destroy)(cudaEvent_t);
+    int (*current_device)();
+};
+_DECX_API_ void set_raw_hooks(const RawHooks* hooks);
 _DECX_API_ bool _is_CUDA_init();
 _DECX_API_ const cudaDeviceProp& _get_cuda_prop();
 }  // namespace cuda
@@ -128,7 +144,26 @@ _DECX_API_ int _device_malloc(decx::PtrInfo<void>* p, uint64_t bytes, bool set_z
 _DECX_API_ int _device_realloc(decx::PtrInfo<void>* p, uint64_t bytes, bool set_zero = false, decx::cuda_stream* S = nullptr);
 _DECX_API_ void _device_dealloc(decx::PtrInfo<void>* p);
 _DECX_API_ void _device_malloc_same_place(decx::PtrInfo<void>* p);   // share: one more reference to p->block
+
+// Block-level interface other DECX modules link against (reference: srcs/modules/core/decx_alloc_interface.h:45-96).
+// Pool of the current device; 0 on success, -1 on failure.
+_DECX_API_ int _alloc_D(decx::MemBlock** _ptr, size_t req_size);
+_DECX_API_ void _alloc_D_same_place(decx::MemBlock** _ptr);
+_DECX_API_ void _dealloc_D(decx::MemBlock* _ptr);
+_DECX_API_ void Memset_D(decx::MemBlock* _ptr, const size_t size, const int value, cudaStream_t* S);
 }  // namespace alloc
+
+// Generic cached resources with a lifespan (reference: decx::ResourceCheckIn/Lock/Unlock/CheckOut,
+// srcs/modules/core/resources_manager/decx_resource.h:67-76, ResMgr.cxx:86-125).  *exposed_ptr is an object the
+// caller built; once it has been unlocked and idle for lifespan_sec the collector thread calls _decon(*exposed_ptr)
+// -- which must free it -- and sets *exposed_ptr to NULL, so the caller rebuilds it on next use.  Lock / Unlock
+// are "in use" marks for the collector (Unlock restarts the idle clock), not mutual exclusion between users.
+typedef void (*res_release_fn)(void*);
+_DECX_API_ uint64_t ResourceCheckIn(void** exposed_ptr, const time_t lifespan_sec, res_release_fn _decon);
+_DECX_API_ void ResourceLock(const uint64_t res_id);
+_DECX_API_ void ResourceUnlock(const uint64_t res_id);
+_DECX_API_ void ResourceCheckOut(const uint64_t res_id);
+namespace alloc {}
 
 // ------------------------------------------------------------------------------------------------ resources
 // Cache of rebuildable scratch with a lifespan (reference: decx::ResourceHandle / decx::ResMgr,
@@ -238,6 +273,52 @@ public:
     virtual de::_DATA_FORMATS_ Format() const;
     virtual ~_GPU_Matrix();
     uint32_t Pitch() const { return _layout.pitch; }
+};
+
+// ------------------------------------------------------------------------------------------------ vectors
+// (reference: decx::_Vector srcs/common/Classes/Vector.h:118-180, decx::_GPU_Vector GPU_Vector.h:77-140)
+class _DECX_API_ _Vector : public de::Vector {
+public:
+    uint64_t length = 0, _length = 0, total_bytes = 0;      // logical, padded to 8 elements, bytes of the padding
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    int _single_element_size = 0;
+    bool _init = false, _pinned = false;
+    void* data = nullptr;           // 64-byte aligned, zero-filled
+    int* _shared = nullptr;
+
+    _Vector();
+    _Vector(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+    void re_construct(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+
+    virtual size_t Len() const;
+    virtual void release();
+    virtual de::Vector& SoftCopy(de::Vector& src);
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual ~_Vector();
+};
+
+class _DECX_API_ _GPU_Vector : public de::GPU_Vector {
+public:
+    uint64_t length = 0, _length = 0, total_bytes = 0;      // padded to 4 elements
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    int _single_element_size = 0;
+    bool _init = false;
+    int _device = -1;
+    decx::PtrInfo<void> Vec;
+
+    _GPU_Vector();
+    _GPU_Vector(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+    void re_construct(const de::_DATA_TYPES_FLAGS_ type, uint64_t length);
+
+    virtual size_t Len() const;
+    virtual void release();
+    virtual de::GPU_Vector& SoftCopy(de::GPU_Vector& src);
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual ~_GPU_Vector();
 };
 
 }  // namespace decx

@@ -237,3 +237,24 @@ void decx::alloc::_device_dealloc(decx::PtrInfo<void>* p) {
 void decx::alloc::_device_malloc_same_place(decx::PtrInfo<void>* p) {
     if (p->block != nullptr) p->block->pool->register_reference(p->block);
 }
+
+// ------------------------------------------------------------------------------------------------ block-level interface
+int decx::alloc::_alloc_D(decx::MemBlock** _ptr, size_t req_size) {
+    if (_ptr == nullptr) return -1;
+    return decx::MemPool_D::GetInstance(current_device())->allocate(req_size, _ptr) == 0 ? 0 : -1;
+}
+
+void decx::alloc::_alloc_D_same_place(decx::MemBlock** _ptr) {
+    if (_ptr != nullptr && *_ptr != nullptr) (*_ptr)->pool->register_reference(*_ptr);
+}
+
+void decx::alloc::_dealloc_D(decx::MemBlock* _ptr) {
+    if (_ptr != nullptr) _ptr->pool->deallocate(_ptr);
+}
+
+void decx::alloc::Memset_D(decx::MemBlock* _ptr, const size_t size, const int value, cudaStream_t* S) {
+    if (_ptr == nullptr || _ptr->ptr == nullptr) return;
+    const size_t n = size < _ptr->size ? size : size_t(_ptr->size);
+    if (S != nullptr) cudaMemsetAsync(_ptr->ptr, value, n, *S);
+    else cudaMemset(_ptr->ptr, value, n);
+}

@@ -8,6 +8,9 @@
 #include "DECX/classes/DecxNumber.h"
 #include "DECX/classes/Matrix.h"
 #include "DECX/classes/GPU_Matrix.h"
+#include "DECX/classes/Vector.h"
+#include "DECX/classes/GPU_Vector.h"
 #include "DECX/classes/decx_memcpy.h"
 #include "DECX/BLAS/BLAS.h"
+#include "DECX/basic_proc/type_cast.h"
 #endif

@@ -29,8 +29,10 @@ extern "C" {
 /* element types; the values are de::_DATA_TYPES_FLAGS_
  * (reference: srcs/includes/DECX/classes/type_info.h:20-43) */
 #define DECXB200_FP32 1
+#define DECXB200_FP64 2
 #define DECXB200_FP16 3
 #define DECXB200_CPLXF 5
+#define DECXB200_CPLXD 6
 
 #define DECXB200_EINVAL (-1)       /* null pointer, zero extent, unknown dtype            */
 #define DECXB200_EALIGN (-2)       /* fp16 operand pitch/base not 16-byte aligned (TMA)    */
@@ -40,10 +42,11 @@ extern "C" {
 #define DECXB200_EKERNEL (-6)      /* the kernel reported a time-out through its status word */
 
 /*
- * Scratch bytes decxb200_gemm needs for one problem (0 for fp16).
+ * Scratch bytes decxb200_gemm needs for one problem (0 for fp16 and fp64).
  * fp32:  tf32 (hi, lo) planes of A and B.
  * cplxf: (hi, lo) planes of A viewed as M x 2K reals and of the 2K x 2N real
  *        expansion of B.
+ * cplxd: the 2K x 2N real expansion of B (doubles).
  * Replaces the planner-owned A-transpose scratch of the reference
  * (srcs/modules/BLAS/GEMM/CUDA/large_squares/common/cuda_GEMM_LS_planner.cu:125-127,156-163).
  */
@@ -67,6 +70,10 @@ DECXB200_API size_t decxb200_gemm_workspace_bytes(int dtype, uint32_t M, uint32_
  * callers behind it (fp32/GEMM_fp32_callers.cuh:75-215, fp16/GEMM_fp16_callers.cuh:57-128,
  * 64b/GEMM_64b_callers.cuh:78-98).  fp16 accumulates in fp32 and stores fp16.
  * fp32 and cplxf run as 3xTF32 and keep fp32 accuracy.
+ * fp64 and cplxd (the remaining cases of the reference's dtype switch, GEMM_LS.cu:335-345; kernels
+ * large_squares/64b/GEMM_fp64_B64_kernels.cu:58, cplxd/GEMM_cplxd_B64_kernels.cu:60) run on the fp64 tensor
+ * path (warp-level DMMA); their alpha / beta are host pointers to double (double[2] for cplxd) and `status`
+ * is not used (the kernel has no waits that could expire).
  */
 DECXB200_API int decxb200_gemm(int dtype, void* stream, uint32_t M, uint32_t N, uint32_t K,
                                const void* A, uint64_t lda, const void* B, uint64_t ldb,
@@ -145,6 +152,50 @@ DECXB200_API int decxb200_gemm_fp32_noalloc(void* stream, uint32_t M, uint32_t N
                                             const void* A, uint64_t lda, const void* B, uint64_t ldb,
                                             const void* C, uint64_t ldc, void* D, uint64_t ldd,
                                             const void* alpha, const void* beta, unsigned* status);
+
+/*
+ * Matrix-vector products: the Vector overloads of de::blas::cuda::GEMM
+ * (reference: srcs/includes/DECX/BLAS/BLAS.h:79-80, drivers srcs/modules/BLAS/GEMM/CUDA/VMM.cu:55-184, kernels
+ * extreme_shapes/VMM_fp32.cu, VMM_fp16.cu).  A is rows x cols, row-major, lda elements per row; device pointers.
+ *   trans == 0:  y[rows] = A . x[cols]      (Matrix x Vector)
+ *   trans == 1:  y[cols] = x[rows] . A      (Vector x Matrix)
+ * dtype DECXB200_FP32 (fp32 result) or DECXB200_FP16 with the reference's three accumulation levels
+ * (srcs/common/Classes/classes_util.h:287-300): L1 = fp32 arithmetic and an fp32 RESULT vector, L2 = fp32
+ * arithmetic and an fp16 result, L3 = fp16 arithmetic throughout and an fp16 result.
+ * One pass over A; skinny shapes cut the reduction into slices whose partial vectors go through `workspace`
+ * (decxb200_gemv_workspace_bytes, 16-byte aligned; without it the call still works, one slice, slower) and are
+ * added in slice order: results do not depend on timing.  Asynchronous on `stream`.
+ */
+#define DECXB200_FP16_ACCU_L1 0
+#define DECXB200_FP16_ACCU_L2 1
+#define DECXB200_FP16_ACCU_L3 2
+DECXB200_API size_t decxb200_gemv_workspace_bytes(int dtype, int fp16_accu, int trans, uint32_t rows, uint32_t cols);
+DECXB200_API int decxb200_gemv(int dtype, int fp16_accu, int trans, void* stream, uint32_t rows, uint32_t cols,
+                               const void* A, uint64_t lda, const void* x, void* y,
+                               void* workspace, size_t workspace_bytes);
+
+/*
+ * dst (cols x rows, ldd) = transpose of src (rows x cols, lds); elements of 1, 2, 4, 8 or 16 bytes; pitches in
+ * elements.  Reference: de::cuda::Transpose, srcs/modules/BLAS/Basic_process/transpose/transpose.cu:50-101.
+ */
+DECXB200_API int decxb200_transpose(int elem_bytes, void* stream, uint32_t rows, uint32_t cols,
+                                    const void* src, uint64_t lds, void* dst, uint64_t ldd);
+
+/*
+ * Element type cast of a pitched rows x cols matrix.  Reference: de::cuda::TypeCast,
+ * srcs/modules/BLAS/Basic_process/type_cast/GPU_Matrix_type_cast.cu:38-85 (fp32<->fp64, int32->fp32); the
+ * fp32<->fp16 pair has no counterpart there -- the reference can only make fp16 operands element by element on
+ * the host (de::Float2Half).  Float narrowing rounds to nearest even; fp32->int32 rounds to nearest even and
+ * saturates.
+ */
+#define DECXB200_CAST_F32_F16 0
+#define DECXB200_CAST_F16_F32 1
+#define DECXB200_CAST_F32_F64 2
+#define DECXB200_CAST_F64_F32 3
+#define DECXB200_CAST_I32_F32 4
+#define DECXB200_CAST_F32_I32 5
+DECXB200_API int decxb200_cast2d(int kind, void* stream, uint32_t rows, uint32_t cols,
+                                 const void* src, uint64_t lds, void* dst, uint64_t ldd);
 
 /*
  * Peer-visible device buffers for the row-sharded multi-GPU GEMM (one process per GPU).

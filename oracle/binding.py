@@ -31,7 +31,8 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(ORACLE_SO):
+        srcs = [os.path.join(HERE, f) for f in ("gemm_oracle.c", "blas_oracle.c")]
+        if not os.path.exists(ORACLE_SO) or any(os.path.getmtime(f) > os.path.getmtime(ORACLE_SO) for f in srcs):
             build()
         L = ctypes.CDLL(ORACLE_SO)
         u32, sz, vp, d, f = ctypes.c_uint32, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_double, ctypes.c_float
@@ -44,6 +45,11 @@ def lib():
         L.oracle_half_to_float.argtypes = [vp, vp, sz]
         L.oracle_float_to_half.argtypes = [vp, vp, sz]
         L.oracle_set_threads.argtypes = [ctypes.c_int]
+        ci = ctypes.c_int
+        L.oracle_gemv_f32.argtypes = [ci, u32, u32, vp, sz, vp, vp]
+        L.oracle_gemv_f16.argtypes = [ci, u32, u32, vp, sz, vp, vp, vp, vp]
+        L.oracle_gemm_f64.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, d, d, vp, sz]
+        L.oracle_gemm_c64.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, vp, vp, vp, sz]
         _lib = L
     return _lib
 
@@ -83,6 +89,37 @@ def gemm(A, B, C=None, alpha=1.0, beta=0.0):
         D = np.empty((M, N), dtype=np.float32)
         L.oracle_gemm_f16(M, N, K, _p(A), K, _p(B), N, _p(C), N, float(alpha), float(beta), _p(D), N)
         return D
+    if A.dtype == np.float64:
+        A, B, C = _c(A, np.float64), _c(B, np.float64), _c(C, np.float64)
+        D = np.empty((M, N), dtype=np.float64)
+        L.oracle_gemm_f64(M, N, K, _p(A), K, _p(B), N, _p(C), N, float(alpha), float(beta), _p(D), N)
+        return D
+    if A.dtype == np.complex128:
+        A, B, C = _c(A, np.complex128), _c(B, np.complex128), _c(C, np.complex128)
+        D = np.empty((M, N), dtype=np.complex128)
+        al = np.array([complex(alpha).real, complex(alpha).imag], dtype=np.float64)
+        be = np.array([complex(beta).real, complex(beta).imag], dtype=np.float64)
+        L.oracle_gemm_c64(M, N, K, _p(A), K, _p(B), N, _p(C), N, _p(al), _p(be), _p(D), N)
+        return D
+    raise TypeError(A.dtype)
+
+
+def gemv(A, x, trans=False):
+    """Oracle matrix-vector product.  float32 -> float64 result.  float16 -> (fp32-accumulated result in index
+    order, fp64-accumulated result, sum of |products| per output) for the three accumulation levels' checks."""
+    L = lib()
+    rows, cols = A.shape
+    n = cols if trans else rows
+    if A.dtype == np.float32:
+        A, x = _c(A, np.float32), _c(x, np.float32)
+        y = np.empty(n, dtype=np.float64)
+        L.oracle_gemv_f32(int(trans), rows, cols, _p(A), cols, _p(x), _p(y))
+        return y
+    if A.dtype == np.float16:
+        A, x = _c(A, np.float16), _c(x, np.float16)
+        y32, y64, mag = np.empty(n, np.float32), np.empty(n, np.float64), np.empty(n, np.float64)
+        L.oracle_gemv_f16(int(trans), rows, cols, _p(A), cols, _p(x), _p(y32), _p(y64), _p(mag))
+        return y32, y64, mag
     raise TypeError(A.dtype)
 
 
@@ -100,11 +137,16 @@ def metric(D, Dref, A, B):
     M, K = A.shape
     N = B.shape[1]
     cplx = int(np.iscomplexobj(A))
-    Af = np.ascontiguousarray(A.astype(np.complex64 if cplx else np.float32))
-    Bf = np.ascontiguousarray(B.astype(np.complex64 if cplx else np.float32))
-    rn = np.empty(M, dtype=np.float64)
-    cn = np.empty(N, dtype=np.float64)
-    L.oracle_norms_f32(M, N, K, cplx, _p(Af), K, _p(Bf), N, _p(rn), _p(cn))
+    if A.dtype in (np.float64, np.complex128):          # 64-bit operands: norms in numpy (float32 would overflow less
+        rn = np.sqrt((np.abs(A) ** 2).sum(axis=1))      # gracefully and lose the scale of tiny values)
+        cn = np.sqrt((np.abs(B) ** 2).sum(axis=0))
+        rn, cn = np.ascontiguousarray(rn, dtype=np.float64), np.ascontiguousarray(cn, dtype=np.float64)
+    else:
+        Af = np.ascontiguousarray(A.astype(np.complex64 if cplx else np.float32))
+        Bf = np.ascontiguousarray(B.astype(np.complex64 if cplx else np.float32))
+        rn = np.empty(M, dtype=np.float64)
+        cn = np.empty(N, dtype=np.float64)
+        L.oracle_norms_f32(M, N, K, cplx, _p(Af), K, _p(Bf), N, _p(rn), _p(cn))
     wide = np.complex128 if cplx else np.float64
     Dw = np.ascontiguousarray(D.astype(wide))
     Rw = np.ascontiguousarray(Dref.astype(wide))

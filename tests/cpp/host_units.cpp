@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <chrono>
+#include <thread>
 #include <vector>
 
 #include "DECX.h"
@@ -205,6 +207,134 @@ static void test_reconstruct_never_keeps_another_devices_block() {
     decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
 }
 
+// ------------------------------------------------------------------------------------------------ stream / event pools
+static int g_fake_dev = 0, g_streams_made = 0, g_streams_gone = 0, g_events_made = 0, g_events_gone = 0;
+static int fake_stream_create(cudaStream_t* s, unsigned) { *s = reinterpret_cast<cudaStream_t>(uintptr_t(0x1000 + ++g_streams_made)); return 0; }
+static int fake_stream_destroy(cudaStream_t) { ++g_streams_gone; return 0; }
+static int fake_event_create(cudaEvent_t* e, unsigned) { *e = reinterpret_cast<cudaEvent_t>(uintptr_t(0x2000 + ++g_events_made)); return 0; }
+static int fake_event_destroy(cudaEvent_t) { ++g_events_gone; return 0; }
+static int fake_current_device() { return g_fake_dev; }
+
+static void test_stream_event_pools() {
+    const decx::cuda::RawHooks hooks = {fake_stream_create, fake_stream_destroy, fake_event_create, fake_event_destroy, fake_current_device};
+    decx::cuda::set_raw_hooks(&hooks);
+    decx::cuda_stream* a = decx::cuda::get_cuda_stream_ptr(1);
+    decx::cuda_stream* b = decx::cuda::get_cuda_stream_ptr(1);
+    CHECK(a != nullptr && b != nullptr && a != b && a->_is_occupied && decx::cuda::pooled_stream_count() == 2);
+    a->detach();
+    decx::cuda_stream* c = decx::cuda::get_cuda_stream_ptr(1);
+    CHECK(c == a && g_streams_made == 2);                            // an idle stream with the same flag is reused
+    decx::cuda_stream* d = decx::cuda::get_cuda_stream_ptr(0);
+    CHECK(d != a && d != b && d->_flag == 0 && g_streams_made == 3); // another flag: a new stream
+    c->detach();
+    g_fake_dev = 1;
+    decx::cuda_stream* e = decx::cuda::get_cuda_stream_ptr(1);
+    CHECK(e != a && e->_device == 1 && g_streams_made == 4);         // never a stream of another device
+    g_fake_dev = 0;
+    decx::cuda_stream& r = decx::cuda::get_cuda_stream_ref(1);
+    CHECK(&r == a);                                                  // the reference form draws from the same pool
+    decx::cuda_event* e1 = decx::cuda::get_cuda_event_ptr(2);
+    e1->detach();
+    decx::cuda_event* e2 = decx::cuda::get_cuda_event_ptr(2);
+    CHECK(e1 == e2 && g_events_made == 1 && decx::cuda::pooled_event_count() == 1);
+    decx::cuda::release_stream_event_pools();
+    CHECK(g_streams_gone == 4 && g_events_gone == 1 && decx::cuda::pooled_stream_count() == 0);
+    decx::cuda::set_raw_hooks(nullptr);
+}
+
+// ------------------------------------------------------------------------------------------------ resource lifespans
+static int g_released = 0;
+static void release_int(void* p) { delete static_cast<int*>(p); ++g_released; }
+
+static void sleep_ms(int ms) { std::this_thread::sleep_for(std::chrono::milliseconds(ms)); }
+
+static void test_resource_lifespans() {
+    // generic resources (the reference's ResourceCheckIn family): collected only when unlocked and idle
+    void* obj = new int(7);
+    const uint64_t id = decx::ResourceCheckIn(&obj, 1, release_int);
+    decx::ResourceLock(id);
+    sleep_ms(1600);
+    CHECK(obj != nullptr && g_released == 0);                        // in use: survives its lifespan
+    decx::ResourceUnlock(id);                                        // idle clock restarts here
+    sleep_ms(400);
+    decx::ResourceLock(id);                                          // users look at the object only while it is locked
+    CHECK(obj != nullptr);
+    decx::ResourceUnlock(id);
+    sleep_ms(1800);
+    decx::ResourceLock(id);
+    CHECK(obj == nullptr && g_released == 1);                        // idle for more than 1 s: released, pointer cleared
+    decx::ResourceUnlock(id);
+    void* obj2 = new int(8);
+    const uint64_t id2 = decx::ResourceCheckIn(&obj2, 100, release_int);
+    decx::ResourceCheckOut(id2);
+    CHECK(obj2 == nullptr && g_released == 2);                       // check-out releases at once
+    decx::ResourceCheckOut(id2);                                     // and is idempotent
+    CHECK(g_released == 2);
+
+    // the GEMM workspace cache: a block of the device pool goes back after its lifespan
+    decx::MemPool_D::set_raw_allocator(fake_alloc, fake_free);
+    decx::MemPool_D* pool = decx::MemPool_D::GetInstance(0);         // CPU run: cudaGetDevice fails, ordinal 0 is used
+    {
+        decx::ScratchResource cache(0.2);
+        void* p = cache.lock(5000, 0);
+        CHECK(p != nullptr && pool->bytes_in_use() >= 5000 && cache.capacity() == 5000);   // capacity(): only while locked
+        sleep_ms(700);
+        CHECK(pool->bytes_in_use() >= 5000);                         // locked: the collector must not take it
+        cache.unlock();
+        void* q = cache.lock(4000, 0);
+        CHECK(q == p);                                               // still cached, large enough: same block
+        cache.unlock();
+        sleep_ms(900);
+        CHECK(pool->bytes_in_use() == 0);                            // idle > 0.2 s: back in the pool
+        void* r = cache.lock(6000, 0);
+        CHECK(r != nullptr && cache.capacity() == 6000);             // rebuilt on next use
+        cache.unlock();
+        cache.release_now();
+        CHECK(pool->bytes_in_use() == 0);
+    }
+    pool->release();
+    decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
+}
+
+static void test_block_level_allocator() {
+    decx::MemPool_D::set_raw_allocator(fake_alloc, fake_free);
+    decx::MemPool_D* pool = decx::MemPool_D::GetInstance(0);
+    decx::MemBlock* b = nullptr;
+    CHECK(decx::alloc::_alloc_D(&b, 3000) == 0 && b != nullptr && b->size == 3072);
+    decx::alloc::_alloc_D_same_place(&b);
+    decx::alloc::_dealloc_D(b);
+    CHECK(pool->bytes_in_use() == 3072);                             // one holder left
+    decx::alloc::_dealloc_D(b);
+    CHECK(pool->bytes_in_use() == 0);
+    pool->release();
+    decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
+}
+
+static void test_vectors() {
+    de::Vector& v = de::CreateVectorRef(de::_FP32_, 13);
+    CHECK(v.Len() == 13 && v.Type() == de::_FP32_);
+    decx::_Vector* iv = dynamic_cast<decx::_Vector*>(&v);
+    CHECK(iv != nullptr && iv->_length == 16 && iv->total_bytes == 64 && reinterpret_cast<uintptr_t>(iv->data) % 64 == 0);
+    for (int i = 0; i < 13; ++i) CHECK(*v.ptr<float>(i) == 0.f);
+    *v.ptr<float>(12) = 5.f;
+    de::Vector& w = de::CreateVectorRef();
+    w.SoftCopy(v);
+    CHECK(w.Len() == 13 && *w.ptr<float>(12) == 5.f);
+    v.release();
+    CHECK(*w.ptr<float>(12) == 5.f);                                 // shared storage outlives the first holder
+    w.Reinterpret(de::_FP16_);
+    CHECK(w.Len() == 26 && w.Type() == de::_FP16_);
+    w.release();
+    // slot order of the public interface (Len, release, SoftCopy, Type, Reinterpret)
+    de::Vector* p = de::CreateVectorPtr(de::_FP16_, 4);
+    void** vt = *reinterpret_cast<void***>(p);
+    typedef size_t (*len_fn)(const de::Vector*);
+    CHECK(reinterpret_cast<len_fn>(vt[0])(p) == 4);
+    typedef de::_DATA_TYPES_FLAGS_ (*type_fn)(const de::Vector*);
+    CHECK(reinterpret_cast<type_fn>(vt[3])(p) == de::_FP16_);
+    p->release();
+}
+
 int main() {
     test_abi();
     test_pitch_and_host_matrix();
@@ -213,6 +343,10 @@ int main() {
     test_pool();
     test_pool_release_under_live_objects();
     test_reconstruct_never_keeps_another_devices_block();
+    test_stream_event_pools();
+    test_block_level_allocator();
+    test_vectors();
+    test_resource_lifespans();
     if (g_fail == 0) std::printf("host_units: all checks passed\n");
     return g_fail == 0 ? 0 : 1;
 }

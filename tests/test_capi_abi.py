@@ -53,7 +53,7 @@ def test_bad_arguments_are_rejected_without_a_gpu():
     p = ctypes.cast(buf, ctypes.c_void_p)
     args = lambda dt, M, N, K, A, B, D, lda=8, ldb=8, ldd=8: (dt, None, M, N, K, A, lda, B, ldb, None, 0, D, ldd,
                                                               None, None, None, 0, None)
-    assert g(*args(2, 4, 4, 4, p, p, p)) == -1            # unknown dtype
+    assert g(*args(4, 4, 4, 4, p, p, p)) == -1            # unknown dtype (4 = int32: no GEMM)
     assert g(*args(capi.FP32, 0, 4, 4, p, p, p)) == -1    # zero extent
     assert g(*args(capi.FP32, 4, 4, 4, None, p, p)) == -1  # null operand
     assert g(*args(capi.FP32, 4, 4, 4, p, p, p, lda=3)) == -1  # pitch smaller than width

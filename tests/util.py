@@ -17,8 +17,8 @@ def make_inputs(dtype, M, N, K, seed, dist="uniform", with_c=False):
         raise ValueError(dist)
 
     def mk(r, c):
-        if np.dtype(dtype) == np.complex64:
-            return (real(r, c) + 1j * real(r, c)).astype(np.complex64)
+        if np.dtype(dtype).kind == "c":
+            return (real(r, c) + 1j * real(r, c)).astype(dtype)
         return real(r, c).astype(dtype)
 
     A, B = mk(M, K), mk(K, N)
