@@ -46,6 +46,11 @@ def _load():
     lib.decxb200_gemm_host_arena_bytes.argtypes = [ci, u32, u32, u32, ci]
     lib.decxb200_gemm_host.restype = ci
     lib.decxb200_gemm_host.argtypes = [ci, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp, sz, vp]
+    lib.decxb200_gemm_host_multi_arena_bytes.restype = sz
+    lib.decxb200_gemm_host_multi_arena_bytes.argtypes = [ci, ci, u32, u32, u32]
+    lib.decxb200_gemm_host_multi.restype = ci
+    lib.decxb200_gemm_host_multi.argtypes = [ci, ci, ctypes.POINTER(ci), u32, u32, u32, vp, u64, vp, u64, vp, u64,
+                                             ctypes.POINTER(vp), sz]
     lib.decxb200_gemm_fp32_noalloc.restype = ci
     lib.decxb200_gemm_fp32_noalloc.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp]
     lib.decxb200_gemm_fp16_panels.restype = ci
@@ -94,7 +99,8 @@ lib = _load()
 
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
-    "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host",
+    "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host", "decxb200_gemm_host_multi_arena_bytes",
+    "decxb200_gemm_host_multi",
     "decxb200_gemm_fp32_noalloc", "decxb200_gemv_workspace_bytes", "decxb200_gemv", "decxb200_transpose",
     "decxb200_cast2d",
     "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",

@@ -115,6 +115,31 @@ def gemm_host(A, B, C=None, alpha=None, beta=None, out=None, arena=None, status=
     return out
 
 
+def gemm_host_multi(A, B, out=None, devices=None, arenas=None):
+    """Host-matrix fp16 GEMM sharded over several GPUs of this process (``decxb200_gemm_host_multi``).
+
+    A, B, out: CPU tensors (pin them); ``devices``: CUDA ordinals (default: all visible); ``arenas``: one uint8
+    CUDA tensor per device (allocated here when missing).  Synchronous.  Returns (out, arenas)."""
+    if A.is_cuda or B.is_cuda or A.dtype != torch.float16 or B.dtype != torch.float16:
+        raise TypeError("gemm_host_multi takes float16 host tensors")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"A is {M}x{K} but B is {K2}x{N}")
+    if devices is None:
+        devices = list(range(torch.cuda.device_count()))
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype).pin_memory()
+    need = int(capi.lib.decxb200_gemm_host_multi_arena_bytes(capi.FP16, len(devices), M, N, K))
+    if arenas is None or len(arenas) != len(devices) or any(a.numel() < need for a in arenas):
+        arenas = [torch.empty(need, dtype=torch.uint8, device=torch.device("cuda", d)) for d in devices]
+    devs = (ctypes.c_int * len(devices))(*devices)
+    ptrs = (ctypes.c_void_p * len(devices))(*[a.data_ptr() for a in arenas])
+    capi.check(capi.lib.decxb200_gemm_host_multi(capi.FP16, len(devices), devs, M, N, K, A.data_ptr(), _ld(A),
+                                                 B.data_ptr(), _ld(B), out.data_ptr(), _ld(out), ptrs, need))
+    return out, arenas
+
+
 def gemm_raw(dt, M, N, K, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, d_ptr, ldd, alpha=None, beta=None,
              ws_ptr=None, ws_bytes=0, status_ptr=None, stream=0, cta_group=0, max_ctas=0):
     """The C ABI with raw device addresses (used where D lives in another GPU's memory)."""

@@ -6,6 +6,7 @@
 // its error codes; "plan + launch" is one call into the C ABI (include/decx_b200.h), and the planner-owned
 // A-transpose scratch is replaced by the tf32-plane workspace, cached with the reference's 5 s lifespan.
 // Unlike the reference, a failed validation returns before anything is launched, and nothing calls exit().
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/decx_b200.h"
@@ -66,6 +67,19 @@ decx::ScratchResource* workspace_cache() {
 decx::ScratchResource* arena_cache() {
     static decx::ScratchResource* r = new decx::ScratchResource(5.0);
     return r;
+}
+// below this much arithmetic one GPU finishes before several could be set up (DECX_B200_MULTI_MIN_FLOPS overrides)
+double multi_min_flops() {
+    const char* e = getenv("DECX_B200_MULTI_MIN_FLOPS");
+    const double v = e ? atof(e) : 0.0;
+    return v > 0.0 ? v : 4.0e12;
+}
+decx::ScratchResource* multi_arena_cache(int device) {          // one per device for the multi-GPU host path
+    static std::mutex mtx;
+    static decx::ScratchResource* r[64] = {nullptr};
+    std::lock_guard<std::mutex> lk(mtx);
+    if (r[device & 63] == nullptr) r[device & 63] = new decx::ScratchResource(5.0);
+    return r[device & 63];
 }
 
 // one status word per device for the kernels' bounded waits, and a pinned host copy to read it back
@@ -200,6 +214,42 @@ void gemm_host(de::Matrix& A_, de::Matrix& B_, de::Matrix* C_, de::Matrix& dst_)
     if (!dst->_init) return fail(de::DECX_FAIL_ALLOCATION, "error: Fail to allocate memory on RAM");
     int device = 0;
     cudaGetDevice(&device);
+    // Large fp16 products without a C operand are sharded by rows over every visible GPU: each GPU moves its rows
+    // over its own PCIe link and the GPUs complete each other's copy of B over NVLink (decxb200_gemm_host_multi).
+    // DECX_B200_MULTI_GPU=0 keeps the call on the current device; =N caps the number of GPUs used.
+    if (dt == DECXB200_FP16 && C == nullptr && (N % 8) == 0) {
+        static const int cap = [] { const char* e = getenv("DECX_B200_MULTI_GPU"); return e ? atoi(e) : 64; }();
+        int ndev = 0;
+        if (cap > 1 && cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 1 &&
+            2.0 * double(M) * double(N) * double(K) >= multi_min_flops() && M >= 512) {
+            if (ndev > cap) ndev = cap;
+            if (ndev > 16) ndev = 16;
+            const uint32_t tiles = (M + 255) / 256;
+            if (uint32_t(ndev) > tiles) ndev = int(tiles);
+            const size_t each = decxb200_gemm_host_multi_arena_bytes(dt, ndev, M, N, K);
+            int devs[16];
+            void* arenas[16];
+            int got = 0;
+            for (int d = 0; d < ndev; ++d) {
+                devs[d] = (device + d) % ndev;                    // the caller's device first
+                cudaSetDevice(devs[d]);
+                arenas[d] = multi_arena_cache(devs[d])->lock(each, devs[d]);
+                if (arenas[d] == nullptr) break;
+                ++got;
+            }
+            cudaSetDevice(device);
+            int rc = -1;
+            if (got == ndev)
+                rc = decxb200_gemm_host_multi(dt, ndev, devs, M, N, K, A->data, A->Pitch(), B->data, B->Pitch(), dst->data,
+                                              dst->Pitch(), arenas, each);
+            for (int d = 0; d < got; ++d) multi_arena_cache(devs[d])->unlock();
+            if (got == ndev) {
+                if (rc != 0) report_abi_error(rc);
+                return;
+            }
+            cudaGetLastError();                                   // not enough memory somewhere: one GPU does it
+        }
+    }
     StatusWord* sw = status_word(device);
     const size_t need = decxb200_gemm_host_arena_bytes(dt, M, N, K, C ? 1 : 0);
     void* arena = arena_cache()->lock(need, device);

@@ -123,6 +123,28 @@ DECXB200_API int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t 
                                     void* arena, size_t arena_bytes, unsigned* status);
 
 /*
+ * The host-pointer form sharded over several GPUs of this process (fp16, plain D = A.B; no counterpart in the
+ * single-GPU reference -- it is what the host-matrix overloads de::blas::cuda::GEMM(de::Matrix&, ...), which the
+ * reference declares in BLAS.h:69-70 and never defines, use when more than one GPU is visible).
+ * Rows of A and D are dealt to the devices in whole 256-row tiles; every device moves ITS rows over ITS OWN
+ * PCIe link (A up, D down, in row blocks pipelined with the GEMMs) and uploads only its share of B's rows;
+ * the devices then complete each other's copy of B over NVLink from inside the first GEMM kernel
+ * (decxb200_gemm_fp16_fetch: per-panel flags written by the upload streams gate the peer copies), so B crosses
+ * PCIe once in total and never waits for a host-side collective.  Without peer access between the devices
+ * each one uploads all of B itself.  Synchronous: returns when D is complete in host memory.
+ *
+ *   devices: CUDA ordinals, distinct; arenas[i]: device scratch ON devices[i], 256-byte aligned, at least
+ *   decxb200_gemm_host_multi_arena_bytes() bytes each.  N must be a multiple of 8.  Pin the host matrices
+ *   (portable pinning, so that every device sees them as pinned) for full PCIe speed.
+ *   The caller's current device is restored before the call returns.
+ */
+DECXB200_API size_t decxb200_gemm_host_multi_arena_bytes(int dtype, int n_devices, uint32_t M, uint32_t N, uint32_t K);
+DECXB200_API int decxb200_gemm_host_multi(int dtype, int n_devices, const int* devices,
+                                          uint32_t M, uint32_t N, uint32_t K,
+                                          const void* A, uint64_t lda, const void* B, uint64_t ldb,
+                                          void* D, uint64_t ldd, void* const* arenas, size_t arena_bytes);
+
+/*
  * fp32 GEMM for callers that must not allocate.  (No counterpart in the reference, whose GEMM always
  * takes its scratch from the device memory pool.)
  *

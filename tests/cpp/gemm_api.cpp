@@ -52,6 +52,27 @@ template <> struct Ops<de::Half> {
     static constexpr double tol = 1e-2;
 };
 
+template <> struct Ops<double> {
+    static constexpr de::_DATA_TYPES_FLAGS_ type = de::_FP64_;
+    typedef long double wide;
+    static double make() { return double(rnd()) + double(rnd()) * 0x1p-24; }
+    static wide up(double x) { return x; }
+    static double mag(wide x) { return double(fabsl(x)); }
+    static de::Number num(double re, double) { return de::Number(re); }
+    static wide scal(double re, double) { return re; }
+    static constexpr double tol = 1e-13;
+};
+template <> struct Ops<de::CPd> {
+    static constexpr de::_DATA_TYPES_FLAGS_ type = de::_COMPLEX_F64_;
+    typedef std::complex<long double> wide;
+    static de::CPd make() { return de::CPd(double(rnd()) + double(rnd()) * 0x1p-24, double(rnd())); }
+    static wide up(de::CPd x) { return wide(x.real, x.image); }
+    static double mag(wide x) { return double(std::abs(x)); }
+    static de::Number num(double re, double im) { return de::Number(de::CPd(re, im)); }
+    static wide scal(double re, double im) { return wide(re, im); }
+    static constexpr double tol = 1e-13;
+};
+
 // M x N x K problem through the device-matrix overloads (fused when `fused`), and through the host-matrix ones
 template <typename T>
 static void run_case(uint32_t M, uint32_t N, uint32_t K, bool fused, bool host_overload) {
@@ -66,7 +87,7 @@ static void run_case(uint32_t M, uint32_t N, uint32_t K, bool fused, bool host_o
     for (uint32_t i = 0; i < M; ++i) for (uint32_t j = 0; j < N; ++j) *C.ptr<T>(i, j) = O::make();
     const double ar = host_overload ? 1.0 : 0.75, ai = host_overload ? 0.0 : -0.5;
     const double br = host_overload ? 1.0 : -1.25, bi = host_overload ? 0.0 : 0.5;
-    const bool cplx = (O::type == de::_COMPLEX_F32_);
+    const bool cplx = (O::type == de::_COMPLEX_F32_ || O::type == de::_COMPLEX_F64_);
     de::ResetLastError();
     if (host_overload) {
         if (fused) de::blas::cuda::GEMM(A, B, C, D); else de::blas::cuda::GEMM(A, B, D);
@@ -179,6 +200,172 @@ static void error_paths() {
     CHECK(d.Width() == 5 && d.Height() == 4 && de::GetLastError()->error_type == de::DECX_SUCCESS);
 }
 
+// Vector overloads of GEMM (host objects), every accumulation level
+static void gemv_cases() {
+    const uint32_t shapes[][2] = {{1, 1}, {37, 129}, {300, 4099}, {2050, 515}};      // rows, cols of the matrix
+    for (auto& sh : shapes) {
+        const uint32_t rows = sh[0], cols = sh[1];
+        for (int trans = 0; trans < 2; ++trans) {
+            const uint32_t nin = trans ? rows : cols, nout = trans ? cols : rows;
+            // fp32
+            de::Matrix& A = de::CreateMatrixRef(de::_FP32_, cols, rows);
+            de::Vector& x = de::CreateVectorRef(de::_FP32_, nin);
+            de::Vector& y = de::CreateVectorRef();
+            for (uint32_t i = 0; i < rows; ++i) for (uint32_t j = 0; j < cols; ++j) *A.ptr<float>(i, j) = rnd();
+            for (uint32_t i = 0; i < nin; ++i) *x.ptr<float>(i) = rnd();
+            if (trans) de::blas::cuda::GEMM(x, A, y); else de::blas::cuda::GEMM(A, x, y);
+            CHECK(de::GetLastError()->error_type == de::DECX_SUCCESS && y.Len() == nout && y.Type() == de::_FP32_);
+            double worst = 0;
+            for (uint32_t o = 0; o < nout; ++o) {
+                double s = 0, na = 0, nx = 0;
+                for (uint32_t k = 0; k < nin; ++k) {
+                    const double a = trans ? *A.ptr<float>(k, o) : *A.ptr<float>(o, k), v = *x.ptr<float>(k);
+                    s += a * v; na += a * a; nx += v * v;
+                }
+                worst = std::fmax(worst, std::fabs(*y.ptr<float>(o) - s) / (std::sqrt(na * nx) + 1e-300));
+            }
+            CHECK(worst <= 1e-5);
+            A.release(); x.release(); y.release();
+            // fp16, three levels
+            for (uint32_t accu = 0; accu < 3; ++accu) {
+                de::Matrix& Ah = de::CreateMatrixRef(de::_FP16_, cols, rows);
+                de::Vector& xh = de::CreateVectorRef(de::_FP16_, nin);
+                de::Vector& yh = de::CreateVectorRef();
+                for (uint32_t i = 0; i < rows; ++i) for (uint32_t j = 0; j < cols; ++j) *Ah.ptr<de::Half>(i, j) = de::Float2Half(rnd() * 0.1f);
+                for (uint32_t i = 0; i < nin; ++i) *xh.ptr<de::Half>(i) = de::Float2Half(rnd() * 0.1f);
+                if (trans) de::blas::cuda::GEMM(xh, Ah, yh, accu); else de::blas::cuda::GEMM(Ah, xh, yh, accu);
+                CHECK(de::GetLastError()->error_type == de::DECX_SUCCESS && yh.Len() == nout);
+                CHECK(yh.Type() == (accu == 0 ? de::_FP32_ : de::_FP16_));
+                worst = 0;
+                for (uint32_t o = 0; o < nout; ++o) {
+                    double s = 0, na = 0, nx = 0;
+                    for (uint32_t k = 0; k < nin; ++k) {
+                        const double a = de::Half2Float(trans ? *Ah.ptr<de::Half>(k, o) : *Ah.ptr<de::Half>(o, k));
+                        const double v = de::Half2Float(*xh.ptr<de::Half>(k));
+                        s += a * v; na += a * a; nx += v * v;
+                    }
+                    const double got = accu == 0 ? double(*yh.ptr<float>(o)) : double(de::Half2Float(*yh.ptr<de::Half>(o)));
+                    worst = std::fmax(worst, (std::fabs(got - s) - 3e-8) / (std::sqrt(na * nx) + 1e-300));
+                }
+                CHECK(worst <= 1e-2);
+                Ah.release(); xh.release(); yh.release();
+            }
+        }
+    }
+    // error paths
+    de::Matrix& A = de::CreateMatrixRef(de::_FP32_, 8, 4);
+    de::Vector& bad = de::CreateVectorRef(de::_FP32_, 5);
+    de::Vector& y = de::CreateVectorRef();
+    de::blas::cuda::GEMM(A, bad, y);
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_DimsNotMatching);
+    de::Vector& h = de::CreateVectorRef(de::_FP16_, 8);
+    de::blas::cuda::GEMM(A, h, y);
+    CHECK(de::GetLastError()->error_type == de::DECX_FAIL_TYPE_MOT_MATCH);
+}
+
+// de::cuda::Transpose and de::cuda::TypeCast on device matrices, then the fp16 GEMM on the cast operands
+static void transpose_cast_cases() {
+    const uint32_t W = 301, H = 130;
+    de::Matrix& hm = de::CreateMatrixRef(de::_FP32_, W, H);
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) *hm.ptr<float>(i, j) = rnd();
+    de::GPU_Matrix& g = de::CreateGPUMatrixRef(de::_FP32_, W, H);
+    de::Memcpy(hm, g, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_H2D);
+    de::GPU_Matrix& gt = de::CreateGPUMatrixRef();
+    de::DH r = de::cuda::Transpose(g, gt);
+    CHECK(r.error_type == de::DECX_SUCCESS && gt.Width() == H && gt.Height() == W && gt.Type() == de::_FP32_);
+    de::Matrix& back = de::CreateMatrixRef(de::_FP32_, H, W);
+    de::Memcpy(back, gt, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(H, W), de::DECX_MEMCPY_D2H);
+    bool same = true;
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) same = same && (*back.ptr<float>(j, i) == *hm.ptr<float>(i, j));
+    CHECK(same);
+    // fp32 -> fp16 on the device equals the host conversion bit for bit; and back is exact
+    de::GPU_Matrix& gh = de::CreateGPUMatrixRef();
+    r = de::cuda::TypeCast(g, gh, de::CVT_FP32_FP16);
+    CHECK(r.error_type == de::DECX_SUCCESS && gh.Type() == de::_FP16_ && gh.Width() == W && gh.Height() == H);
+    de::Matrix& hh = de::CreateMatrixRef(de::_FP16_, W, H);
+    de::Memcpy(hh, gh, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_D2H);
+    same = true;
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) same = same && (hh.ptr<de::Half>(i, j)->val == de::Float2Half(*hm.ptr<float>(i, j)).val);
+    CHECK(same);
+    de::GPU_Matrix& g2 = de::CreateGPUMatrixRef();
+    r = de::cuda::TypeCast(gh, g2, de::CVT_FP16_FP32);
+    CHECK(r.error_type == de::DECX_SUCCESS && g2.Type() == de::_FP32_);
+    de::Matrix& h2 = de::CreateMatrixRef(de::_FP32_, W, H);
+    de::Memcpy(h2, g2, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_D2H);
+    same = true;
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) same = same && (*h2.ptr<float>(i, j) == de::Half2Float(*hh.ptr<de::Half>(i, j)));
+    CHECK(same);
+    // fp32 <-> fp64
+    de::GPU_Matrix& gd = de::CreateGPUMatrixRef();
+    r = de::cuda::TypeCast(g, gd, de::CVT_FP32_FP64);
+    CHECK(r.error_type == de::DECX_SUCCESS && gd.Type() == de::_FP64_);
+    r = de::cuda::TypeCast(gd, g2, de::CVT_FP64_FP32);
+    de::Memcpy(h2, g2, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(W, H), de::DECX_MEMCPY_D2H);
+    same = true;
+    for (uint32_t i = 0; i < H; ++i) for (uint32_t j = 0; j < W; ++j) same = same && (*h2.ptr<float>(i, j) == *hm.ptr<float>(i, j));
+    CHECK(same);
+    // wrong source type / unknown method
+    r = de::cuda::TypeCast(gh, g2, de::CVT_FP32_FP16);
+    CHECK(r.error_type == de::DECX_FAIL_TYPE_MOT_MATCH);
+    r = de::cuda::TypeCast(g, g2, de::CVT_UINT8_CYCLIC);
+    CHECK(r.error_type == de::DECX_FAIL_INVALID_PARAM);
+    // the cast operand feeds the fp16 GEMM: (H x W) . (W x H)
+    de::GPU_Matrix& ght = de::CreateGPUMatrixRef();
+    de::cuda::Transpose(gh, ght);
+    de::GPU_Matrix& prod = de::CreateGPUMatrixRef();
+    de::ResetLastError();
+    de::blas::cuda::GEMM(gh, ght, prod);
+    CHECK(de::GetLastError()->error_type == de::DECX_SUCCESS && prod.Width() == H && prod.Height() == H);
+    de::Matrix& hp = de::CreateMatrixRef(de::_FP16_, H, H);
+    de::Memcpy(hp, prod, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(H, H), de::DECX_MEMCPY_D2H);
+    double worst = 0;
+    for (uint32_t i = 0; i < H; i += 7)
+        for (uint32_t j = 0; j < H; j += 5) {
+            double s = 0, na = 0, nb = 0;
+            for (uint32_t k = 0; k < W; ++k) {
+                const double a = de::Half2Float(*hh.ptr<de::Half>(i, k)), b = de::Half2Float(*hh.ptr<de::Half>(j, k));
+                s += a * b; na += a * a; nb += b * b;
+            }
+            worst = std::fmax(worst, std::fabs(de::Half2Float(*hp.ptr<de::Half>(i, j)) - s) / std::sqrt(na * nb));
+        }
+    CHECK(worst <= 1e-2);
+}
+
+// Host-matrix fp16 GEMM large enough (threshold lowered through the environment) to be sharded over every visible GPU
+static void multi_gpu_host_case() {
+    setenv("DECX_B200_MULTI_MIN_FLOPS", "1e9", 1);
+    const uint32_t M = 1300, N = 2104, K = 520;
+    de::Matrix& A = de::CreateMatrixRef(de::_FP16_, K, M);
+    de::Matrix& B = de::CreateMatrixRef(de::_FP16_, N, K);
+    de::Matrix& D = de::CreateMatrixRef();
+    for (uint32_t i = 0; i < M; ++i) for (uint32_t j = 0; j < K; ++j) *A.ptr<de::Half>(i, j) = de::Float2Half(rnd() * 0.2f);
+    for (uint32_t i = 0; i < K; ++i) for (uint32_t j = 0; j < N; ++j) *B.ptr<de::Half>(i, j) = de::Float2Half(rnd() * 0.2f);
+    de::cuda::PinMemory(A);
+    de::cuda::PinMemory(B);
+    de::ResetLastError();
+    de::blas::cuda::GEMM(A, B, D);
+    CHECK(de::GetLastError()->error_type == de::DECX_SUCCESS && D.Width() == N && D.Height() == M);
+    double worst = 0;
+    for (uint32_t i = 0; i < M; i += 13)
+        for (uint32_t j = 0; j < N; j += 31) {
+            double s = 0, na = 0, nb = 0;
+            for (uint32_t k = 0; k < K; ++k) {
+                const double a = de::Half2Float(*A.ptr<de::Half>(i, k)), b = de::Half2Float(*B.ptr<de::Half>(k, j));
+                s += a * b; na += a * a; nb += b * b;
+            }
+            worst = std::fmax(worst, std::fabs(de::Half2Float(*D.ptr<de::Half>(i, j)) - s) / std::sqrt(na * nb));
+        }
+    CHECK(worst <= 1e-2);
+    // the same product on one GPU gives the same bits
+    setenv("DECX_B200_MULTI_MIN_FLOPS", "1e30", 1);
+    de::Matrix& D1 = de::CreateMatrixRef();
+    de::blas::cuda::GEMM(A, B, D1);
+    bool same = de::GetLastError()->error_type == de::DECX_SUCCESS;
+    for (uint32_t i = 0; i < M && same; ++i) for (uint32_t j = 0; j < N; ++j) same = same && (D.ptr<de::Half>(i, j)->val == D1.ptr<de::Half>(i, j)->val);
+    CHECK(same);
+    unsetenv("DECX_B200_MULTI_MIN_FLOPS");
+}
+
 int main() {
     de::InitCPUInfo();
     de::InitCuda();
@@ -189,12 +376,18 @@ int main() {
             run_case<float>(s[0], s[1], s[2], fused, false);
             run_case<de::Half>(s[0], s[1], s[2], fused, false);
             run_case<de::CPf>(s[0], s[1], s[2], fused, false);
+            run_case<double>(s[0], s[1], s[2], fused, false);
+            run_case<de::CPd>(s[0], s[1], s[2], fused, false);
         }
     for (int fused = 0; fused < 2; ++fused) {
         run_case<float>(2300, 140, 90, fused, true);      // several row blocks in the host-matrix pipeline
         run_case<de::Half>(300, 136, 72, fused, true);
         run_case<de::CPf>(260, 70, 33, fused, true);
+        run_case<double>(2100, 70, 33, fused, true);
     }
+    gemv_cases();
+    transpose_cast_cases();
+    multi_gpu_host_case();
     sample_known_answer();
     error_paths();
     de::cuda::DECX_CUDA_exit();

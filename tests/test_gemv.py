@@ -75,7 +75,8 @@ def test_gemv_fp16_levels(Bl, dev, shape, trans, accu):
     got = y.cpu().numpy().astype(np.float64)
     scale = _scale(A, x, trans)
     assert y.dtype == (torch.float32 if accu == 0 else torch.float16)
-    assert (np.abs(got - y64) / scale).max() <= 1e-2
+    # fp16 results below 2^-14 are subnormal (absolute spacing 2^-24): allow half a step on top of the metric
+    assert (np.abs(got - y64) <= 1e-2 * scale + (2.0 ** -25 if accu else 0.0)).all()
     if accu == 0:
         # fp32 arithmetic in another summation order: a few fp32 ulps of the summed magnitudes
         assert (np.abs(got - y64) <= 64 * 2.0 ** -24 * mag + 1e-30).all()
