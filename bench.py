@@ -43,6 +43,24 @@ DESCR = {
     "cfg4": "complex fp32 GEMM (3xTF32, 4 real products) M=N=K=4096, U[-1,1]",
     "cfg1": "fp32 GEMM (3xTF32) M=N=K=1024, U[-1,1]",
 }
+# matrix-vector, transpose, cast (HBM-bound: bytes per launch / measured copy bandwidth) and the fp64 GEMMs
+AUX = {
+    # name: (kind, dtype, rows, cols, extra)
+    "gemv_f32_rows": ("gemv", "float32", 16384, 16384, {"trans": False}),
+    "gemv_f32_cols": ("gemv", "float32", 16384, 16384, {"trans": True}),
+    "gemv_f16_rows": ("gemv", "float16", 32768, 16384, {"trans": False, "accu": 0}),
+    "gemv_f16_cols": ("gemv", "float16", 32768, 16384, {"trans": True, "accu": 0}),
+    "gemv_f16_cols_l3": ("gemv", "float16", 32768, 16384, {"trans": True, "accu": 2}),
+    "transpose_f32": ("transpose", "float32", 16384, 16384, {}),
+    "transpose_f16": ("transpose", "float16", 32768, 16384, {}),
+    "transpose_c64": ("transpose", "complex64", 8192, 16384, {}),
+    "cast_f32_f16": ("cast", "float32", 16384, 16384, {"to": "float16"}),
+    "cast_f16_f32": ("cast", "float16", 16384, 16384, {"to": "float32"}),
+    "gemm_f64_4096": ("gemm64", "float64", 4096, 4096, {"K": 4096, "ff": 2}),
+    "gemm_c128_2048": ("gemm64", "complex128", 2048, 2048, {"K": 2048, "ff": 8}),
+}
+FP64_NOMINAL_TFLOPS = 40.0      # B200 datasheet fp64 (vector and tensor); no measured fp64 peak exists for this pool
+
 ARITH = {"float16": "f16 (fp32 accumulate)", "float32": "3xTF32 (fp32 accumulate)", "complex64": "3xTF32 (fp32 accumulate)"}
 
 
@@ -223,6 +241,81 @@ def variant_name(v):
     kind, rest = divmod(v, 100)
     ctas, nacc = divmod(rest, 10)
     return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}>"
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured copy bandwidth"
+    return 6650.0, "fallback copy bandwidth"
+
+
+def time_aux(torch, name, device, iters=10, warmup=3):
+    """One of the AUX workloads: median CUDA-event time of a launch, operands (>= 1 GiB) far larger than L2."""
+    from decx_b200 import blas as Bl, gemm as G
+    kind, dtype, rows, cols, ex = AUX[name]
+    tdt = getattr(torch, dtype)
+    g = torch.Generator(device=device).manual_seed(7)
+    def rnd(shape, dt):
+        if dt.is_complex:
+            return torch.complex(torch.randn(shape, device=device, generator=g), torch.randn(shape, device=device, generator=g)).to(dt)
+        return (torch.randn(shape, device=device, generator=g) * 0.05).to(dt)
+    esz = torch.empty(0, dtype=tdt).element_size()
+    if kind == "gemv":
+        A = rnd((rows, cols), tdt)
+        x = rnd((rows if ex["trans"] else cols,), tdt)
+        accu = ex.get("accu", 0)
+        need = int(capi_lib().decxb200_gemv_workspace_bytes(3 if dtype == "float16" else 1, accu, int(ex["trans"]), rows, cols))
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        out = Bl.gemv(A, x, trans=ex["trans"], fp16_accu=accu, workspace=ws)
+        run = lambda: Bl.gemv(A, x, trans=ex["trans"], fp16_accu=accu, out=out, workspace=ws)
+        work, unit, bound = rows * cols * esz + x.numel() * esz + out.numel() * out.element_size(), "GB/s", "hbm"
+    elif kind == "transpose":
+        A = rnd((rows, cols), tdt)
+        out = torch.empty((cols, rows), dtype=tdt, device=device)
+        run = lambda: Bl.transpose(A, out=out)
+        work, unit, bound = 2 * rows * cols * esz, "GB/s", "hbm"
+    elif kind == "cast":
+        to = getattr(torch, ex["to"])
+        A = rnd((rows, cols), tdt)
+        out = torch.empty((rows, cols), dtype=to, device=device)
+        run = lambda: Bl.cast(A, to, out=out)
+        work, unit, bound = rows * cols * (esz + out.element_size()), "GB/s", "hbm"
+    else:
+        K = ex["K"]
+        A, B = rnd((rows, K), tdt), rnd((K, cols), tdt)
+        out = torch.empty((rows, cols), dtype=tdt, device=device)
+        need = int(capi_lib().decxb200_gemm_workspace_bytes(2 if dtype == "float64" else 6, rows, cols, K))
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        run = lambda: G.gemm(A, B, out=out, workspace=ws)
+        work, unit, bound = ex["ff"] * rows * cols * K, "TFLOP/s", "fp64 tensor (DMMA)"
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize(device)
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ts.append(e0.elapsed_time(e1))
+    med = statistics.median(ts)
+    if unit == "GB/s":
+        achieved = work / (med * 1e-3) / 1e9
+        peak, src = hbm_peak()
+    else:
+        achieved = work / (med * 1e-3) / 1e12
+        peak, src = FP64_NOMINAL_TFLOPS, "nominal B200 fp64 (no measured fp64 peak for this pool)"
+    return {"workload": name, "kind": kind, "dtype": dtype, "rows": rows, "cols": cols, **{k: v for k, v in ex.items()},
+            "ms_median": med, "ms_best": min(ts), "launches_per_call": capi_lib().decxb200_last_launch_count(),
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                         "work_per_launch": work, "peak_source": src}}
+
+
+def capi_lib():
+    from decx_b200 import capi
+    return capi.lib
 
 
 def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
@@ -474,8 +567,12 @@ def main():
                 wp = tensor_peak(WORKLOADS[w][0], pk)
                 r["pct_of_peak"] = 100 * r["tflops"] / wp
                 r["peak_tflops"] = wp
+                r["roofline"] = {"bound": "tensor", "achieved": r["tflops"], "peak": wp, "unit": "TFLOP/s",
+                                 "frac": r["tflops"] / wp, "note": "whole call (pre-passes included) / measured bf16 burst"
+                                 + ("" if WORKLOADS[w][0] == "float16" else " / 6")}
                 others.append(r)
         line["other_configs"] = others
+        line["aux_kernels"] = [time_aux(torch, name, device) for name in AUX]
     sg.close()
     if rank == 0 and not args.no_extras and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.workload)

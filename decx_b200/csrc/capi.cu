@@ -54,10 +54,43 @@ std::mutex g_dev_mutex;
 thread_local int t_variant = 0;    // KIND*100 + CTAS*10 + NACC of the last GEMM kernel this thread launched
 
 
+// Encoded tensor maps are cached per thread, keyed by everything that goes into them (base address, extents,
+// pitch, box, swizzle, rank): a program that multiplies the same matrices again -- a training loop, the row blocks
+// of the host-pointer path, a benchmark -- pays for cuTensorMapEncodeTiled once.  A map only DESCRIBES memory, so a
+// stale entry for a freed and re-allocated address is still correct for the same key.
+struct MapKey {
+    const void* base; uint64_t rows, cols, ld; uint32_t b0, b1, b2; int f16, swizzle, rank;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && b0 == o.b0 && b1 == o.b1 && b2 == o.b2 &&
+               f16 == o.f16 && swizzle == o.swizzle && rank == o.rank;
+    }
+};
+struct MapCache {
+    static constexpr int N = 48;
+    MapKey key[N];
+    CUtensorMap map[N];
+    int used = 0, next = 0;
+    const CUtensorMap* find(const MapKey& k) const {
+        for (int i = 0; i < used; ++i)
+            if (key[i] == k) return &map[i];
+        return nullptr;
+    }
+    void put(const MapKey& k, const CUtensorMap& m) {
+        const int i = used < N ? used++ : (next = (next + 1) % N);
+        key[i] = k;
+        map[i] = m;
+    }
+};
+thread_local MapCache t_maps;
+thread_local unsigned long long t_map_hits = 0, t_map_misses = 0;
+
 // 2-D row-major tensor (rows x cols, `ld` elements per row) with a (box_cols x box_rows) box,
 // 128-byte swizzle (of 16-byte units unless `swizzle` says otherwise), zero fill outside [0, cols) x [0, rows).
 int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
              uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    const MapKey mk = {base, rows, cols, ld, box_cols, box_rows, 0, f16 ? 1 : 0, int(swizzle), 2};
+    if (const CUtensorMap* hit = t_maps.find(mk)) { *map = *hit; ++t_map_hits; return 0; }
+    ++t_map_misses;
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return DECXB200_EDRIVER;
     const uint64_t esz = f16 ? 2 : 4;
@@ -69,6 +102,7 @@ int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) t_maps.put(mk, *map);
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
@@ -80,6 +114,9 @@ int make_map(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64
 // only reaches output columns that are never stored.  Chunks past the last one are zero-filled.
 int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                        uint32_t chunk_cols, uint32_t box_k, uint32_t box_chunks, CUtensorMapSwizzle swizzle) {
+    const MapKey mk = {base, rows, cols, ld, chunk_cols, box_k, box_chunks, f16 ? 1 : 0, int(swizzle), 3};
+    if (const CUtensorMap* hit = t_maps.find(mk)) { *map = *hit; ++t_map_hits; return 0; }
+    ++t_map_misses;
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return DECXB200_EDRIVER;
     const uint64_t esz = f16 ? 2 : 4;
@@ -90,6 +127,7 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
     CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) t_maps.put(mk, *map);
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
@@ -892,6 +930,10 @@ int decxb200_ipc_close(void* peer_ptr) {
 
 int decxb200_last_launch_count(void) { return t_launches; }
 int decxb200_last_kernel_variant(void) { return t_variant; }
+void decxb200_tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+    if (hits != nullptr) *hits = t_map_hits;
+    if (misses != nullptr) *misses = t_map_misses;
+}
 
 const char* decxb200_strerror(int code) {
     switch (code) {

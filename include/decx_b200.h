@@ -306,6 +306,10 @@ DECXB200_API int decxb200_last_launch_count(void);
  * e.g. 22 = fp16 256x512 pair tile, 121 = 3xTF32 256x256 pair tile. */
 DECXB200_API int decxb200_last_kernel_variant(void);
 
+/* Tensor maps (TMA descriptors) are cached per host thread by (address, extents, pitch, box); these are the
+ * calling thread's counts of look-ups served from the cache and of fresh cuTensorMapEncodeTiled calls. */
+DECXB200_API void decxb200_tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
+
 /* Static description of an error code returned by this library. */
 DECXB200_API const char* decxb200_strerror(int code);
 
