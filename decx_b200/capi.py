@@ -51,6 +51,9 @@ def _load():
     lib.decxb200_gemm_host_multi.restype = ci
     lib.decxb200_gemm_host_multi.argtypes = [ci, ci, ctypes.POINTER(ci), u32, u32, u32, vp, u64, vp, u64, vp, u64,
                                              ctypes.POINTER(vp), sz]
+    pu32 = ctypes.POINTER(u32)
+    lib.decxb200_gemm_host_multi_plan.restype = ci
+    lib.decxb200_gemm_host_multi_plan.argtypes = [ci, u32, u32, u32, pu32, pu32, pu32, pu32, pu32, pu32, pu32]
     lib.decxb200_gemm_fp32_noalloc.restype = ci
     lib.decxb200_gemm_fp32_noalloc.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u64, vp, vp, vp]
     lib.decxb200_gemm_fp16_panels.restype = ci
@@ -101,7 +104,7 @@ lib = _load()
 
 EXPORTS = [
     "decxb200_gemm_workspace_bytes", "decxb200_gemm", "decxb200_gemm_ex",
-    "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host", "decxb200_gemm_host_multi_arena_bytes",
+    "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host", "decxb200_gemm_host_multi_arena_bytes", "decxb200_gemm_host_multi_plan",
     "decxb200_gemm_host_multi",
     "decxb200_gemm_fp32_noalloc", "decxb200_gemv_workspace_bytes", "decxb200_gemv", "decxb200_transpose",
     "decxb200_cast2d",

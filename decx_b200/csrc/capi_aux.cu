@@ -133,16 +133,20 @@ int decxb200_transpose(int elem_bytes, void* stream_, uint32_t rows, uint32_t co
                                                                       static_cast<uint8_t*>(dst), ldd, rows, cols);
             break;
         case 2:
-            if ((lds % 2) == 0 && (ldd % 2) == 0 && (sa % 4) == 0 && (da % 4) == 0)
-                transpose_b2_kernel<<<grid(64), 256, 0, s>>>(static_cast<const uint16_t*>(src), lds,
-                                                             static_cast<uint16_t*>(dst), ldd, rows, cols);
+            if ((lds % 8) == 0 && (ldd % 8) == 0 && (sa % 16) == 0 && (da % 16) == 0)
+                transpose_b2_vec_kernel<<<dim3((cols + 127) / 128, (rows + 63) / 64), 256, 0, s>>>(
+                    static_cast<const uint16_t*>(src), lds, static_cast<uint16_t*>(dst), ldd, rows, cols);
             else
                 transpose_scalar_kernel<uint16_t><<<grid(32), 256, 0, s>>>(static_cast<const uint16_t*>(src), lds,
                                                                            static_cast<uint16_t*>(dst), ldd, rows, cols);
             break;
         case 4:
-            transpose_words_kernel<uint32_t, 32><<<grid(32), 256, 0, s>>>(static_cast<const uint32_t*>(src), lds,
-                                                                          static_cast<uint32_t*>(dst), ldd, rows, cols);
+            if ((lds % 4) == 0 && (ldd % 4) == 0 && (sa % 16) == 0 && (da % 16) == 0)
+                transpose_b4_vec_kernel<<<grid(64), 256, 0, s>>>(static_cast<const uint32_t*>(src), lds,
+                                                                 static_cast<uint32_t*>(dst), ldd, rows, cols);
+            else
+                transpose_words_kernel<uint32_t, 32><<<grid(32), 256, 0, s>>>(static_cast<const uint32_t*>(src), lds,
+                                                                              static_cast<uint32_t*>(dst), ldd, rows, cols);
             break;
         case 8:
             transpose_words_kernel<uint64_t, 32><<<grid(32), 256, 0, s>>>(static_cast<const uint64_t*>(src), lds,
@@ -164,8 +168,8 @@ int decxb200_cast2d(int kind, void* stream_, uint32_t rows, uint32_t cols, const
     dxb_host::reset_launches();
     if (src == nullptr || dst == nullptr || rows == 0 || cols == 0 || lds < cols || ldd < cols) return DECXB200_EINVAL;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-    const uint64_t work = uint64_t(rows) * ((cols + 3) / 4);
-    const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 32 ? 148ull * 32 : work / 256 + 1);
+    const uint64_t work = uint64_t(rows) * ((cols + 1) / 2);
+    const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 64 ? 148ull * 64 : work / 256 + 1);
 #define DXB_CAST(KIND)                                                                                              \
     {                                                                                                               \
         using S = CastTypes<KIND>::S;                                                                               \

@@ -148,6 +148,24 @@ size_t decxb200_gemm_host_multi_arena_bytes(int dtype, int n_devices, uint32_t M
     return size_t(make_plan(n_devices, M, N, K).total);
 }
 
+int decxb200_gemm_host_multi_plan(int n_devices, uint32_t M, uint32_t N, uint32_t K, uint32_t* row0, uint32_t* nrows,
+                                  uint32_t* block_rows_out, uint32_t* piece0, uint32_t* piece_rows, uint32_t* n_panels,
+                                  uint32_t* panel_end) {
+    if (n_devices < 1 || n_devices > MAX_MULTI || M == 0 || N == 0 || K == 0) return DECXB200_EINVAL;
+    const Plan p = make_plan(n_devices, M, N, K);
+    for (int d = 0; d < n_devices; ++d) {
+        if (row0) row0[d] = p.row0[d];
+        if (nrows) nrows[d] = p.nrows[d];
+        if (block_rows_out) block_rows_out[d] = p.rb[d];
+        if (piece0) piece0[d] = p.piece0[d];
+        if (piece_rows) piece_rows[d] = p.piece_rows[d];
+    }
+    if (n_panels) *n_panels = p.n_panels;
+    if (panel_end)
+        for (uint32_t j = 0; j < p.n_panels; ++j) panel_end[j] = p.panel_end[j];
+    return 0;
+}
+
 int decxb200_gemm_host_multi(int dtype, int n_devices, const int* devices, uint32_t M, uint32_t N, uint32_t K,
                              const void* A, uint64_t lda, const void* B, uint64_t ldb, void* D, uint64_t ldd,
                              void* const* arenas, size_t arena_bytes) {

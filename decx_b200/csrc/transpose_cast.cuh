@@ -35,43 +35,94 @@ transpose_words_kernel(const W* __restrict__ src, uint64_t lds, W* __restrict__ 
     }
 }
 
-// 2-byte elements: threads move 32-bit words (two elements of a row) and transpose 2 x 2 element blocks in
-// registers, so that both the reads and the writes are 128-byte rows.  Needs even pitches and 4-byte aligned
-// bases (the caller checks); odd extents are handled element-wise at the edges.
+// 4-byte elements, 16-byte global accesses: a CTA moves a 64 x 64 block; a thread loads four float4 (rows 16
+// apart), scatters them into the padded tile, then gathers four elements of one tile COLUMN (conflict-free with the
+// 65-word row stride) into one float4 of a dst row.  Needs 16-byte aligned bases and pitches that are multiples
+// of 4 elements (the caller checks); ragged edges fall back to element accesses inside the kernel.
 __global__ void __launch_bounds__(256)
-transpose_b2_kernel(const uint16_t* __restrict__ src, uint64_t lds, uint16_t* __restrict__ dst, uint64_t ldd,
-                    uint32_t rows, uint32_t cols) {
-    // tile: 64 x 64 elements = 32 x 32 blocks of 2 x 2
-    __shared__ uint32_t even[32][33], odd[32][33];    // [block column][block row]: words of dst rows 2j and 2j+1
-    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+transpose_b4_vec_kernel(const uint32_t* __restrict__ src, uint64_t lds, uint32_t* __restrict__ dst, uint64_t ldd,
+                        uint32_t rows, uint32_t cols) {
+    __shared__ uint32_t tile[64][65];
+    const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 vectors across, 16 rows down
     const uint32_t r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-        const uint32_t bi = ty + i;                               // block row
-        const uint32_t r = r0 + 2 * bi, c = c0 + 2 * tx;
-        uint32_t w0 = 0, w1 = 0;
-        if (c < cols) {
-            // a word may take in the padding element after the last column: the pitch is even, so it exists
-            if (r < rows) w0 = __ldcs(reinterpret_cast<const uint32_t*>(src + uint64_t(r) * lds + c));
-            if (r + 1 < rows) w1 = __ldcs(reinterpret_cast<const uint32_t*>(src + uint64_t(r + 1) * lds + c));
+    for (int i = 0; i < 64; i += 16) {
+        const uint32_t r = r0 + ty + i, c = c0 + 4 * tx;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) {
+            const uint32_t* p = src + uint64_t(r) * lds + c;
+            if (c + 4 <= cols) v = __ldcs(reinterpret_cast<const uint4*>(p));
+            else {
+                if (c + 0 < cols) v.x = p[0];
+                if (c + 1 < cols) v.y = p[1];
+                if (c + 2 < cols) v.z = p[2];
+            }
         }
-        even[tx][bi] = __byte_perm(w0, w1, 0x5410);               // (src[r][c], src[r+1][c])
-        odd[tx][bi] = __byte_perm(w0, w1, 0x7632);                // (src[r][c+1], src[r+1][c+1])
+        tile[ty + i][4 * tx + 0] = v.x;
+        tile[ty + i][4 * tx + 1] = v.y;
+        tile[ty + i][4 * tx + 2] = v.z;
+        tile[ty + i][4 * tx + 3] = v.w;
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-        const uint32_t bj = ty + j;                               // block column of src = pair of dst rows
-        const uint32_t dc = r0 + 2 * tx;                          // dst column (= src row) of the word
-        if (dc >= rows) continue;
+    for (int i = 0; i < 64; i += 16) {
+        const uint32_t tc = ty + i;                                   // tile column = dst row
+        const uint32_t dr = c0 + tc, dc = r0 + 4 * tx;
+        if (dr >= cols || dc >= rows) continue;
+        const uint4 v = make_uint4(tile[4 * tx + 0][tc], tile[4 * tx + 1][tc], tile[4 * tx + 2][tc], tile[4 * tx + 3][tc]);
+        uint32_t* p = dst + uint64_t(dr) * ldd + dc;
+        if (dc + 4 <= rows) __stcs(reinterpret_cast<uint4*>(p), v);
+        else {
+            p[0] = v.x;
+            if (dc + 1 < rows) p[1] = v.y;
+            if (dc + 2 < rows) p[2] = v.z;
+        }
+    }
+}
+
+// 2-byte elements, 16-byte global accesses.  A CTA moves 64 rows x 128 columns.  A thread loads eight elements of
+// two consecutive rows (two uint4), transposes the four 2 x 2 blocks in registers -- byte_perm turns the words
+// (a0 a1), (b0 b1) into (a0 b0) and (a1 b1) -- and stores the words by [column pair][row pair]; the write phase
+// gathers four consecutive row pairs of one dst row into a uint4.  Needs 16-byte aligned bases and pitches that are
+// multiples of 8 elements; ragged extents are handled element-wise at the edges, pitch padding is never written.
+__global__ void __launch_bounds__(256)
+transpose_b2_vec_kernel(const uint16_t* __restrict__ src, uint64_t lds, uint16_t* __restrict__ dst, uint64_t ldd,
+                        uint32_t rows, uint32_t cols) {
+    __shared__ uint32_t even[64][33], odd[64][33];     // [column pair][row pair]: words of dst rows 2cp and 2cp + 1
+    const uint32_t r0 = blockIdx.y * 64, c0 = blockIdx.x * 128;
+    {
+        const uint32_t v = threadIdx.x & 15, rp0 = threadIdx.x >> 4;   // vector of 8 columns, row pair
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t dr = c0 + 2 * bj + h;
-            if (dr >= cols) continue;
-            const uint32_t w = h ? odd[bj][tx] : even[bj][tx];
-            uint16_t* p = dst + uint64_t(dr) * ldd + dc;
-            if (dc + 1 < rows) __stcs(reinterpret_cast<uint32_t*>(p), w);
-            else *p = uint16_t(w & 0xffffu);                      // odd row count: the last element alone
+        for (int i = 0; i < 32; i += 16) {
+            const uint32_t rp = rp0 + i, r = r0 + 2 * rp, c = c0 + 8 * v;
+            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+            if (c < cols) {     // a vector may take in pitch padding after the last column: lds is a multiple of 8
+                if (r < rows) a = __ldcs(reinterpret_cast<const uint4*>(src + uint64_t(r) * lds + c));
+                if (r + 1 < rows) b = __ldcs(reinterpret_cast<const uint4*>(src + uint64_t(r + 1) * lds + c));
+            }
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                even[4 * v + j][rp] = __byte_perm(aw[j], bw[j], 0x5410);
+                odd[4 * v + j][rp] = __byte_perm(aw[j], bw[j], 0x7632);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t idx = threadIdx.x + 256 * i;
+        const uint32_t vec = idx & 7, drow = idx >> 3;                // 8 vectors of 8 elements per dst row, 128 dst rows
+        const uint32_t dr = c0 + drow, dc = r0 + 8 * vec;
+        if (dr >= cols || dc >= rows) continue;
+        const uint32_t (*t)[33] = (drow & 1) ? odd : even;
+        const uint32_t cp = drow >> 1;
+        const uint4 w = make_uint4(t[cp][4 * vec + 0], t[cp][4 * vec + 1], t[cp][4 * vec + 2], t[cp][4 * vec + 3]);
+        uint16_t* p = dst + uint64_t(dr) * ldd + dc;
+        if (dc + 8 <= rows) __stcs(reinterpret_cast<uint4*>(p), w);
+        else {
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            for (uint32_t e = 0; e < 8 && dc + e < rows; ++e) p[e] = uint16_t(ww[e >> 1] >> (16 * (e & 1)));
         }
     }
 }
@@ -121,7 +172,8 @@ template <> __device__ __forceinline__ float cast1<CAST_I32_F32>(int32_t v) { re
 template <> __device__ __forceinline__ int32_t cast1<CAST_F32_I32>(float v) { return __float2int_rn(v); }
 
 // rows x cols, pitched both sides.  A thread converts G consecutive elements, G chosen so that the wider side
-// moves 32 bytes and the narrower 16 (or 8): vector accesses when `vec_ok`, element-wise on the ragged tail.
+// moves 16 bytes per access and the narrower one 8 (or 16): every load and store instruction of a warp then
+// covers one contiguous span (no half-written sectors).  Vector accesses when `vec_ok`, element-wise on the tail.
 template <int KIND>
 __global__ void __launch_bounds__(256)
 cast2d_kernel(const typename CastTypes<KIND>::S* __restrict__ src, uint64_t lds,
@@ -129,7 +181,7 @@ cast2d_kernel(const typename CastTypes<KIND>::S* __restrict__ src, uint64_t lds,
     using S = typename CastTypes<KIND>::S;
     using D = typename CastTypes<KIND>::D;
     constexpr int WIDE = sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D);
-    constexpr int G = 32 / WIDE;                                  // 8 (4-byte wide side) or 4 (8-byte wide side)
+    constexpr int G = 16 / WIDE;                                  // 4 (4-byte wide side) or 2 (8-byte wide side)
     const uint32_t groups = (cols + G - 1) / G;
     const uint64_t total = uint64_t(rows) * groups;
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
@@ -139,21 +191,12 @@ cast2d_kernel(const typename CastTypes<KIND>::S* __restrict__ src, uint64_t lds,
         if (vec_ok && c + G <= cols) {
             S in[G];
             D out[G];
-            constexpr int SV = G * sizeof(S) / 16, DV = G * sizeof(D) / 16;   // 16-byte vectors per side (>= 1 ... 2)
-            if constexpr (SV >= 1) {
-#pragma unroll
-                for (int v = 0; v < SV; ++v) reinterpret_cast<uint4*>(in)[v] = __ldcs(reinterpret_cast<const uint4*>(s) + v);
-            } else {
-                *reinterpret_cast<uint2*>(in) = __ldcs(reinterpret_cast<const uint2*>(s));
-            }
+            if constexpr (G * sizeof(S) == 16) *reinterpret_cast<uint4*>(in) = __ldcs(reinterpret_cast<const uint4*>(s));
+            else *reinterpret_cast<uint2*>(in) = __ldcs(reinterpret_cast<const uint2*>(s));
 #pragma unroll
             for (int e = 0; e < G; ++e) out[e] = cast1<KIND>(in[e]);
-            if constexpr (DV >= 1) {
-#pragma unroll
-                for (int v = 0; v < DV; ++v) __stcs(reinterpret_cast<uint4*>(d) + v, reinterpret_cast<const uint4*>(out)[v]);
-            } else {
-                __stcs(reinterpret_cast<uint2*>(d), *reinterpret_cast<const uint2*>(out));
-            }
+            if constexpr (G * sizeof(D) == 16) __stcs(reinterpret_cast<uint4*>(d), *reinterpret_cast<const uint4*>(out));
+            else __stcs(reinterpret_cast<uint2*>(d), *reinterpret_cast<const uint2*>(out));
         } else {
             for (int e = 0; e < G && c + e < cols; ++e) d[e] = cast1<KIND>(s[e]);
         }

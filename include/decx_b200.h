@@ -139,6 +139,13 @@ DECXB200_API int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t 
  *   The caller's current device is restored before the call returns.
  */
 DECXB200_API size_t decxb200_gemm_host_multi_arena_bytes(int dtype, int n_devices, uint32_t M, uint32_t N, uint32_t K);
+/* The partition decxb200_gemm_host_multi uses, for inspection (arrays of n_devices entries, panel_end of 16; any
+ * pointer may be NULL): rows of A / D per device and the height of its row blocks, the rows of B each device
+ * uploads, and the column panels (exclusive ends) in which B is completed. */
+DECXB200_API int decxb200_gemm_host_multi_plan(int n_devices, uint32_t M, uint32_t N, uint32_t K,
+                                               uint32_t* row0, uint32_t* nrows, uint32_t* block_rows,
+                                               uint32_t* piece0, uint32_t* piece_rows,
+                                               uint32_t* n_panels, uint32_t* panel_end);
 DECXB200_API int decxb200_gemm_host_multi(int dtype, int n_devices, const int* devices,
                                           uint32_t M, uint32_t N, uint32_t K,
                                           const void* A, uint64_t lda, const void* B, uint64_t ldb,

@@ -79,3 +79,30 @@ def test_front_end_refuses_host_tensors_and_missing_gpu():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):
             G.gemm_host(torch.zeros(4, 4), torch.zeros(4, 4))
+
+
+def test_multi_gpu_host_plan_partitions_rows_pieces_and_panels():
+    """The planner of the in-process multi-GPU host GEMM, on the CPU: rows of A in whole 256-row tiles, B's rows
+    dealt once over the devices that have work, panels that tile the columns on 512-column boundaries."""
+    u32 = ctypes.c_uint32
+    for n, M, N, K in ((1, 300, 520, 70), (2, 1300, 2104, 520), (8, 65536, 16384, 16384), (4, 520, 1024, 256),
+                       (8, 700, 40000, 2053), (3, 100000, 8, 16)):
+        row0, nrows, rb, p0, pr = ((u32 * n)() for _ in range(5))
+        npan, pend = u32(), (u32 * 16)()
+        assert capi.lib.decxb200_gemm_host_multi_plan(n, M, N, K, row0, nrows, rb, p0, pr, ctypes.byref(npan), pend) == 0
+        assert sum(nrows) == M and row0[0] == 0
+        covered = 0
+        for d in range(n):
+            if nrows[d]:
+                assert row0[d] == covered and row0[d] % 256 == 0 and 0 < rb[d] <= nrows[d]
+                assert rb[d] == nrows[d] or rb[d] % 256 == 0
+                covered += nrows[d]
+        pieces = sorted((p0[d], pr[d]) for d in range(n) if nrows[d])
+        assert pieces[0][0] == 0 and sum(r for _, r in pieces) == K          # every row of B uploaded exactly once
+        assert all(a[0] + a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+        assert all(pr[d] == 0 for d in range(n) if not nrows[d])             # idle devices upload nothing
+        ends = list(pend[: npan.value])
+        assert 1 <= npan.value <= 16 and ends[-1] == N and ends == sorted(set(ends))
+        assert all(e % 512 == 0 for e in ends[:-1])
+        assert capi.lib.decxb200_gemm_host_multi_arena_bytes(capi.FP16, n, M, N, K) > K * N * 2
+    assert capi.lib.decxb200_gemm_host_multi_plan(0, 1, 1, 1, None, None, None, None, None, None, None) == -1
