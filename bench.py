@@ -190,7 +190,7 @@ def run_reference(args, rank, world, emit):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (AVX2 FMA)", "data": "synthetic",
         "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
-                   "step": info["sample"]},
+                   "parallelism": f"rows of A over {args.gpus} GPU(s)", "l2": "n/a (host cores)", "sample": info["sample"]},
         "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": info["cores"], "kind": info["kind"],
                          "sample": info["sample"], "host_cpus": info["host_cpus"]},
         "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -318,13 +318,27 @@ def capi_lib():
     return capi.lib
 
 
-def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
-    """Kernel-level timing of one single-GPU configuration (device-resident operands)."""
+def pitched(torch, t):
+    """Copy of a 2-D tensor in DECX's device-matrix layout: rows start 128 bytes apart or more
+    (srcs/modules/core/classes/GPU_Matrix.cu:35-61), which is what de::GPU_Matrix hands to the GEMM."""
+    r, c = t.shape
+    e = t.element_size()
+    pc = ((c * e + 127) // 128 * 128) // e
+    if pc == c:
+        return t
+    buf = torch.zeros((r, pc), dtype=t.dtype, device=t.device)
+    buf[:, :c] = t
+    return buf[:, :c]
+
+
+def time_single(torch, G, capi, workload, device, iters=7, warmup=3, cooldown_s=1.0):
+    """Kernel-level timing of one single-GPU configuration: device-resident operands in DECX's pitched layout,
+    each call timed alone with CUDA events after a short idle (the denominators were measured the same way)."""
     dtype, M, N, K, dist_name, sigma, fused, ff = WORKLOADS[workload]
-    A = gen(torch, (M, K), dtype, dist_name, sigma, device, 100)
-    B = gen(torch, (K, N), dtype, dist_name, sigma, device, 101)
-    C = gen(torch, (M, N), dtype, dist_name, sigma, device, 102) if fused else None
-    out = torch.empty((M, N), dtype=A.dtype, device=device)
+    A = pitched(torch, gen(torch, (M, K), dtype, dist_name, sigma, device, 100))
+    B = pitched(torch, gen(torch, (K, N), dtype, dist_name, sigma, device, 101))
+    C = pitched(torch, gen(torch, (M, N), dtype, dist_name, sigma, device, 102)) if fused else None
+    out = pitched(torch, torch.zeros((M, N), dtype=A.dtype, device=device))
     need = capi.workspace_bytes(G._DTYPES[A.dtype], M, N, K)
     ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
     st = G.new_status(device)
@@ -332,6 +346,7 @@ def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
     for _ in range(warmup):
         run()
     torch.cuda.synchronize(device)
+    time.sleep(cooldown_s)
     ts = []
     for _ in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -345,7 +360,36 @@ def time_single(torch, G, capi, workload, device, iters=5, warmup=3):
     med = statistics.median(ts)
     return {"workload": workload, "description": DESCR[workload], "ms_median": med, "ms_best": min(ts),
             "tflops": flops / med / 1e9, "tflops_best": flops / min(ts) / 1e9,
-            "launches_per_call": capi.lib.decxb200_last_launch_count(), "arithmetic": ARITH[dtype]}
+            "launches_per_call": capi.lib.decxb200_last_launch_count(), "arithmetic": ARITH[dtype],
+            "layout": "row pitch = width rounded up to 128 bytes (DECX device matrices)", "cooldown_s": cooldown_s,
+            "kernel": variant_name(capi.lib.decxb200_last_kernel_variant())}
+
+
+def like_for_like_cpu(workload, rows=256):
+    """The reference's CPU GEMM on rows 0..rows-1 of the same fp32 / complex-fp32 configuration (same arithmetic type on
+    both sides), one child process, best of 2."""
+    from oracle import binding as ob
+    dtype, M, N, K, _, sigma, _, ff = WORKLOADS[workload]
+    if dtype == "float16" or not ob.ref_available():
+        return None
+    rows = min(rows, M)
+    r = ob.ref_cpu_gemm_time(5 if dtype == "complex64" else 1, rows, N, K, threads=16, repeats=2, sigma=sigma)
+    best = min(r["times"])
+    return {"value": ff * rows * N * K / best / 1e12, "unit": "TFLOPS", "cores": r["threads"], "kind": "reference",
+            "sample": f"de::blas::cpu::GEMM on rows 0..{rows - 1} ({rows}x{N}x{K}), best of 2 calls", "seconds": best}
+
+
+def cfg1_cpu_reference():
+    """BASELINE configuration 1 as written: fp32 1024^3 through the reference's de::blas::cpu::GEMM on this host's
+    cores, best of 50 calls after warm-up (one child process)."""
+    from oracle import binding as ob
+    if not ob.ref_available():
+        return None
+    r = ob.ref_cpu_gemm_time(1, 1024, 1024, 1024, threads=16, repeats=52, sigma=1.0)
+    ts = sorted(r["times"][2:])
+    return {"workload": "cfg1", "ms_best": ts[0] * 1e3, "ms_median": ts[len(ts) // 2] * 1e3, "calls": len(ts),
+            "gflops_best": 2 * 1024 ** 3 / ts[0] / 1e9, "threads": r["threads"], "host_cpus": os.cpu_count(),
+            "what": "de::blas::cpu::GEMM fp32 M=N=K=1024, inputs N(0,1) seeded (the reference's generator cannot be seeded)"}
 
 
 def main():
@@ -550,7 +594,8 @@ def main():
         "vs_baseline": None, "dtype": ARITH[dtype], "data": "synthetic (seeded, generated on the device)",
         "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
                    "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, overlap={sg.overlap}, gather={sg.gather}" if world > 1 else ""),
-                   "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30)},
+                   "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30),
+                   "sample": "the whole problem, every step"},
         "pct_of_peak": {"value": 100 * value / (world * peak), "denominator_tflops": world * peak,
                         "which": f"{pk['source']} bf16 burst x {world} GPU(s)" + ("" if dtype == "float16" else ", /2 for TF32, /3 for 3xTF32"),
                         "of_sustained": (100 * value / (world * pk["bf16_sustained"] / (1 if dtype == "float16" else 6))) if pk["bf16_sustained"] else None},
@@ -575,22 +620,24 @@ def main():
                 r["roofline"] = {"bound": "tensor", "achieved": r["tflops"], "peak": wp, "unit": "TFLOP/s",
                                  "frac": r["tflops"] / wp, "note": "whole call (pre-passes included) / measured bf16 burst"
                                  + ("" if WORKLOADS[w][0] == "float16" else " / 6")}
+                if rank == 0 and w in ("cfg2", "cfg4"):
+                    r["cpu_baseline"] = like_for_like_cpu(w)
                 others.append(r)
         line["other_configs"] = others
         line["aux_kernels"] = [time_aux(torch, name, device) for name in AUX]
     sg.close()
     if rank == 0 and not args.no_extras and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.workload)
+        line["cpu_cfg1_reference"] = cfg1_cpu_reference()
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
         emit(line)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu
-# captures summarised under profiles/ (None = not captured for that configuration)
-# fp16 16384^3: 6.71 GB read + 0.53 GB written (profiles/gemm_tcgen05_f16_16384x16384x16384.md); config 5 has
-# 4x the row slabs at the same N and K, so 4x the traffic per launch; fp32 8192^3 from its own capture.
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from one ncu capture per kernel
+# (None = not captured for that configuration).  fp16 16384^3: 6.71 GB read + 0.53 GB written; config 5 has four
+# times the row slabs at the same N and K, so four times the traffic per launch; fp32 8192^3 from its own capture.
 TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 7.24e9, ("cfg5", 1): 29.0e9, ("cfg2", 1): 4.83e9}
 
 if __name__ == "__main__":

@@ -93,6 +93,8 @@ def _load():
     lib.decxb200_last_kernel_variant.argtypes = []
     lib.decxb200_tensor_map_cache_stats.restype = None
     lib.decxb200_tensor_map_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)]
+    lib.decxb200_debug_stats.restype = ci
+    lib.decxb200_debug_stats.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
     lib.decxb200_strerror.restype = ctypes.c_char_p
     lib.decxb200_strerror.argtypes = [ci]
     lib.decxb200_version.restype = ctypes.c_char_p
@@ -110,7 +112,7 @@ EXPORTS = [
     "decxb200_cast2d",
     "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
-    "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_tensor_map_cache_stats", "decxb200_strerror", "decxb200_version",
+    "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_tensor_map_cache_stats", "decxb200_debug_stats", "decxb200_strerror", "decxb200_version",
 ]
 
 

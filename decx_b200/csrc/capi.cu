@@ -137,11 +137,17 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
     // that is what makes the stores efficient when D lives in another GPU's memory; DECXB200_TMA_STORE=0 disables
     static const int tma_store_env = [] { const char* e = getenv("DECXB200_TMA_STORE"); return e ? atoi(e) : 1; }();
-    CUtensorMap dmap = a0;
+    CUtensorMap dmap = a0, cmap = a0;
     p.d_tma = 0;
+    p.c_tma = 0;
     if (tma_store_env && p.vec_d) {
         const bool f16 = (KIND == 0);
         if (make_map(&dmap, f16, p.D, p.M, p.N, p.ldd, f16 ? 64 : 32, 32) == 0) p.d_tma = 1;
+        // C through the same staging tile (TMA load, same box and swizzle) when its rows are 16-byte aligned too
+        static const int tma_c_env = [] { const char* e = getenv("DECXB200_TMA_C"); return e ? atoi(e) : 1; }();
+        if (p.d_tma && tma_c_env && p.C != nullptr && p.vec_c &&
+            make_map(&cmap, f16, p.C, p.M, p.N, p.ldc, f16 ? 64 : 32, 32) == 0)
+            p.c_tma = 1;
     }
     using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
     auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC, FETCH>;
@@ -213,7 +219,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, p, f);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, cmap, p, f);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
     t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0);
@@ -308,10 +314,19 @@ int prep_b(cudaStream_t stream, bool cplx, const void* B, uint64_t ldb, uint32_t
     return e == cudaSuccess ? 0 : int(e);
 }
 
+// Timing record of the GEMM kernels for tuning sessions (DECXB200_STATS=1): the kernels add to it, the host reads
+// and clears it through decxb200_debug_stats.  Off by default: no kernel touches it then.
+__device__ unsigned long long g_debug_stats[32];
+
 void fill_common(GemmParams& p, const Scalars& sc, const void* C, void* D, unsigned* status) {
     memset(&p, 0, sizeof(p));
     p.D = D;
     p.status = status;
+    static const int stats_env = [] { const char* e = getenv("DECXB200_STATS"); return e ? atoi(e) : 0; }();
+    if (stats_env) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_debug_stats) == cudaSuccess) p.stats = static_cast<unsigned long long*>(addr);
+    }
     // every wait inside the kernels gives up after this long (DECXB200_WAIT_LIMIT_MS, default 4 s)
     static const unsigned long long limit_ns = [] {
         const char* e = getenv("DECXB200_WAIT_LIMIT_MS");
@@ -930,6 +945,14 @@ int decxb200_ipc_close(void* peer_ptr) {
 
 int decxb200_last_launch_count(void) { return t_launches; }
 int decxb200_last_kernel_variant(void) { return t_variant; }
+int decxb200_debug_stats(unsigned long long out[32]) {
+    if (out == nullptr) return DECXB200_EINVAL;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_debug_stats, sizeof(unsigned long long) * 32);   // waits for earlier kernels
+    if (e != cudaSuccess) return int(e);
+    static const unsigned long long zeros[32] = {0};
+    e = cudaMemcpyToSymbol(g_debug_stats, zeros, sizeof(zeros));
+    return e == cudaSuccess ? 0 : int(e);
+}
 void decxb200_tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses) {
     if (hits != nullptr) *hits = t_map_hits;
     if (misses != nullptr) *misses = t_map_misses;

@@ -86,6 +86,7 @@ struct GemmParams {
     int vec_d, vec_c;          // 1 if 16-byte vector access to D / C rows is legal
     int d_tma;                 // 1: D is written by TMA bulk stores from a shared-memory staging tile (128-byte rows,
                                //    edges clipped in hardware); 0: predicated per-thread stores
+    int c_tma;                 // 1 (needs d_tma): boxes of C are brought into the staging tile by TMA loads (tmC)
     int b_chunked_map;         // 1: the B maps are 3-D (column, k, 128-byte chunk): one TMA fetches a whole stage
                                // 0: 2-D maps, one TMA per 128-byte column chunk
     uint32_t tiles_m, tiles_n; // in units of (128*CTAS) x 256
@@ -106,7 +107,9 @@ struct GemmParams {
     unsigned sync_limit_ns;    // how long a producer waits for the others before it goes on alone
     // optional timing record (device memory, zeroed by the host; nullptr = off), in ns of %globaltimer:
     //   [0..15] when panel i was complete (couriers), [16] start of CTA 0, [17] latest CTA end,
-    //   [18] sum over the loaders of the time spent waiting for panel flags, [19] number of such waits
+    //   [18] sum over the loaders of the time spent waiting for panel flags, [19] number of such waits,
+    //   [20] sum over the MMA threads of the time spent waiting for operands (full barriers), [21] ... for a free
+    //   accumulator, [22] ... of their whole tile loops, [23] number of MMA threads counted
     unsigned long long* stats;
 };
 
@@ -179,6 +182,7 @@ struct GemmCfg {
     static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * FETCH;
     static constexpr int STAGING = EPI_WARPS * 4096;      // per epilogue warp: 32 rows x 128 bytes of output
     static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(16 * STAGES + 32 + 8 + 16 + 8 * EPI_WARPS <= 256, "barrier area");
     static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
 };
 
@@ -210,12 +214,15 @@ __device__ __forceinline__ void report(const GemmParams& p, unsigned code) {
 
 template <int KIND>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, float (&acc)[32],
-                                            uint32_t stage_row = 0, uint32_t unit0 = 0) {
+                                            uint32_t stage_row = 0, uint32_t unit0 = 0, bool c_staged = false) {
     // acc holds the fp32 accumulators of columns col0 .. col0+31 of `row` (clobbered).
     // stage_row == 0: write them to D (the caller guarantees row < M).
     // stage_row != 0: shared-memory address of this thread's 128-byte row of the warp's staging tile; the
     //   values go there (16-byte units unit0.., 128-byte swizzle) and a TMA store writes the tile later.  Rows
     //   at or beyond M are staged too (TMA drops them) but never read C.
+    // c_staged: a TMA load has put this box of C into the staging tile (same units, same swizzle); C is read from
+    //   there, unit by unit, right before the unit is overwritten with the result -- instead of 16-byte global
+    //   loads that touch 32 different rows per warp instruction.
     const bool has_c = (p.C != nullptr) && (row < p.M);
     const uint32_t ncols = min(32u, p.N - col0);
     const uint32_t sw = (stage_row >> 7) & 7u;               // row index within the 8-row swizzle atom
@@ -226,10 +233,11 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
         const bool scale = has_c || p.alpha_re != 1.0f;
         if (scale) {
             if (has_c) {
-                if (ncols == 32 && p.vec_c) {
+                if (c_staged || (ncols == 32 && p.vec_c)) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const uint4 c4 = __ldg(reinterpret_cast<const uint4*>(crow) + q);
+                        const uint4 c4 = c_staged ? ld_shared_v4(stage_row + (((unit0 + q) ^ sw) << 4))
+                                                  : __ldg(reinterpret_cast<const uint4*>(crow) + q);
                         const __half2* h = reinterpret_cast<const __half2*>(&c4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -276,10 +284,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
         const float* crow = has_c ? reinterpret_cast<const float*>(p.C) + size_t(row) * p.ldc + col0 : nullptr;
         if (p.epi_mode == EPI_REAL) {
             if (has_c) {
-                if (ncols == 32 && p.vec_c) {
+                if (c_staged || (ncols == 32 && p.vec_c)) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        const float4 c4 = __ldg(reinterpret_cast<const float4*>(crow) + q);
+                        float4 c4;
+                        if (c_staged) {
+                            const uint4 u = ld_shared_v4(stage_row + (((unit0 + q) ^ sw) << 4));
+                            c4 = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+                        } else {
+                            c4 = __ldg(reinterpret_cast<const float4*>(crow) + q);
+                        }
                         acc[4 * q + 0] = p.alpha_re * acc[4 * q + 0] + p.beta_re * c4.x;
                         acc[4 * q + 1] = p.alpha_re * acc[4 * q + 1] + p.beta_re * c4.y;
                         acc[4 * q + 2] = p.alpha_re * acc[4 * q + 2] + p.beta_re * c4.z;
@@ -299,17 +313,29 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
             const bool scale = has_c || p.alpha_re != 1.0f || p.alpha_im != 0.0f;
             if (scale) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float re = acc[i], im = acc[i + 1];
-                    float ore = p.alpha_re * re - p.alpha_im * im;
-                    float oim = p.alpha_re * im + p.alpha_im * re;
-                    if (has_c && i < ncols) {
-                        const float2 c2 = __ldg(reinterpret_cast<const float2*>(crow + i));
-                        ore += p.beta_re * c2.x - p.beta_im * c2.y;
-                        oim += p.beta_re * c2.y + p.beta_im * c2.x;
+                for (int q = 0; q < 8; ++q) {                // one 16-byte unit = two complex numbers
+                    float cc[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (has_c) {
+                        if (c_staged) {
+                            const uint4 u = ld_shared_v4(stage_row + (((unit0 + q) ^ sw) << 4));
+                            cc[0] = __uint_as_float(u.x); cc[1] = __uint_as_float(u.y);
+                            cc[2] = __uint_as_float(u.z); cc[3] = __uint_as_float(u.w);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; e += 2)
+                                if (uint32_t(4 * q + e) < ncols) {
+                                    const float2 c2 = __ldg(reinterpret_cast<const float2*>(crow + 4 * q + e));
+                                    cc[e] = c2.x; cc[e + 1] = c2.y;
+                                }
+                        }
                     }
-                    acc[i] = ore;
-                    acc[i + 1] = oim;
+#pragma unroll
+                    for (int e = 0; e < 4; e += 2) {
+                        const int i = 4 * q + e;
+                        const float re = acc[i], im = acc[i + 1];
+                        acc[i] = p.alpha_re * re - p.alpha_im * im + p.beta_re * cc[e] - p.beta_im * cc[e + 1];
+                        acc[i + 1] = p.alpha_re * im + p.alpha_im * re + p.beta_re * cc[e + 1] + p.beta_im * cc[e];
+                    }
                 }
             }
         }
@@ -435,7 +461,8 @@ template <int KIND, int CTAS, int NACC, int FETCH>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                    const __grid_constant__ CUtensorMap tmD, const GemmParams p, const FetchParams f) {
+                    const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmC, const GemmParams p,
+                    const FetchParams f) {
     using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
     constexpr int STAGES = Cfg::STAGES;
 
@@ -449,6 +476,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const uint32_t accf_bar = bar_base + 16 * STAGES;        // 2 x 8 B  accumulator full
     const uint32_t acce_bar = accf_bar + 16;                 // 2 x 8 B  accumulator empty
     const uint32_t tmem_slot = acce_bar + 16;                // 4 B
+    const uint32_t cbar_base = acce_bar + 24;                // EPI_WARPS x 8 B: arrival of a box of C in a warp's staging tile
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -475,6 +503,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             mbar_init(accf_bar + 8 * a, 1);
             mbar_init(acce_bar + 8 * a, Cfg::ACC_ARRIVALS);
         }
+        for (int w = 0; w < Cfg::EPI_WARPS; ++w) mbar_init(cbar_base + 8 * w, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -594,14 +623,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             const uint32_t peer_accf = (CTAS == 2) ? map_to_cta(accf_bar, 1) : 0u;
             uint32_t s = 0, ph = 0, it = 0;          // `it` counts accumulation chains (chunks)
             bool ok = true;
+            const bool timed = p.stats != nullptr;
+            uint64_t w_full = 0, w_acc = 0;
+            const uint64_t t_loop = timed ? global_timer_ns() : 0;
 
             for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
                 for (uint32_t c = 0; c < n_chunks && ok; ++c, ++it) {
                     // NACC 1: chains alternate between the two TMEM accumulators; NACC 2: a tile owns both
                     const uint32_t a = (NACC == 2) ? 0u : (it & 1u);
                     const uint32_t aph = (NACC == 2) ? (it & 1u) : ((it >> 1) & 1u);
+                    const uint64_t ta = timed ? global_timer_ns() : 0;
                     bool freed = mbar_wait_bounded(acce_bar + 8 * a, aph ^ 1u, limit);
                     if (NACC == 2 && freed) freed = mbar_wait_bounded(acce_bar + 8, aph ^ 1u, limit);
+                    if (timed) w_acc += global_timer_ns() - ta;
                     if (!freed) {
                         report(p, KS_TIMEOUT_MMA_ACC);
                         ok = false;
@@ -611,7 +645,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     const uint32_t d_tmem = tmem_base + a * Cfg::BN;
                     const uint32_t kb_end = min(n_kb, (c + 1) * chunk_kb);
                     for (uint32_t kb = c * chunk_kb; kb < kb_end; ++kb) {
-                        if (!mbar_wait_bounded(full_bar + 8 * s, ph, limit)) {
+                        const uint64_t tf = timed ? global_timer_ns() : 0;
+                        const bool filled = mbar_wait_bounded(full_bar + 8 * s, ph, limit);
+                        if (timed) w_full += global_timer_ns() - tf;
+                        if (!filled) {
                             report(p, KS_TIMEOUT_MMA_FULL);
                             ok = false;
                             break;
@@ -653,6 +690,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     }
                 }
             }
+            if (timed) {
+                atomicAdd(p.stats + 20, (unsigned long long)w_full);
+                atomicAdd(p.stats + 21, (unsigned long long)w_acc);
+                atomicAdd(p.stats + 22, (unsigned long long)(global_timer_ns() - t_loop));
+                atomicAdd(p.stats + 23, 1ull);
+            }
             // tail: both accumulators drained by every epilogue warp (of both CTAs)
             if (ok) {
                 for (int i = 0; i < 2; ++i) {
@@ -678,6 +721,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         const uint32_t stage_row = p.d_tma ? stage_warp + lane * 128u : 0u;
         constexpr uint32_t BOX_COLS = 128 / ((KIND == 0) ? 2 : 4);        // output columns per 128-byte row
         if (p.d_tma && lane == 0) tma_prefetch_desc(&tmD);
+        if (p.c_tma && lane == 0) tma_prefetch_desc(&tmC);
+        const uint32_t cbar = cbar_base + 8 * (warp - 2u);
+        uint32_t cph = 0;                                    // phase of cbar
+        // Brings the box of C at (box_col, box_row) into this warp's staging tile; every lane returns once the
+        // data is there.  The previous TMA store must already have finished reading the tile.
+        auto fetch_c_box = [&](uint32_t box_col, uint32_t box_row) -> bool {
+            if (lane == 0) {
+                mbar_arrive_expect_tx(cbar, 4096u);
+                tma_load_2d(stage_warp, &tmC, cbar, int32_t(box_col), int32_t(box_row));
+            }
+            const bool got = mbar_wait_bounded(cbar, cph, limit);
+            cph ^= 1u;
+            return got;
+        };
         // TMA drops rows at or beyond M exactly, but it was seen to clip the column edge in 16-byte units, so a box
         // that crosses an edge N which is not 16-byte aligned is written by predicated per-thread stores instead
         const bool ragged_n = ((p.N * ((KIND == 0) ? 2u : 4u)) & 15u) != 0u;
@@ -730,7 +787,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                             if (p.d_tma && !(ragged_n && col0 + BOX_COLS > p.N)) {
                                 if (lane == 0) bulk_wait_read_all();     // the previous box has left the staging tile
                                 __syncwarp();
-                                store_chunk<KIND>(p, row, col0, part, stage_row, 0);
+                                const bool c_box = p.c_tma && warp_row0 < p.M;
+                                if (c_box && !fetch_c_box(col0, warp_row0)) {
+                                    if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                                    ok = false;
+                                    break;
+                                }
+                                store_chunk<KIND>(p, row, col0, part, stage_row, 0, c_box);
                                 fence_proxy_async_smem();
                                 __syncwarp();
                                 if (lane == 0 && warp_row0 < p.M) {
@@ -772,11 +835,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     if (p.d_tma && !(ragged_n && box_col0 + BOX_COLS > p.N)) {
                         // two 32-column chunks fill one 64-column (128-byte) box of fp16 output
                         const uint32_t half = c & (BOX_COLS / 32 - 1);
+                        const uint32_t warp_row0_c = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32;
+                        const bool c_box = p.c_tma && warp_row0_c < p.M;
                         if (half == 0) {
                             if (lane == 0) bulk_wait_read_all();         // the previous box has left the staging tile
                             __syncwarp();
+                            if (c_box && !fetch_c_box(box_col0, warp_row0_c)) {
+                                if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                                ok = false;
+                                break;
+                            }
                         }
-                        store_chunk<KIND>(p, row, col0, acc, stage_row, half * 4);
+                        store_chunk<KIND>(p, row, col0, acc, stage_row, half * 4, c_box);
                         if (half == BOX_COLS / 32 - 1 || col0 + 32 >= p.N) {
                             const uint32_t warp_row0 = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32;
                             fence_proxy_async_smem();

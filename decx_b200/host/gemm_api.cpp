@@ -6,8 +6,10 @@
 // its error codes; "plan + launch" is one call into the C ABI (include/decx_b200.h), and the planner-owned
 // A-transpose scratch is replaced by the tf32-plane workspace, cached with the reference's 5 s lifespan.
 // Unlike the reference, a failed validation returns before anything is launched, and nothing calls exit().
+#include <condition_variable>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/decx_b200.h"
 #include "internal.h"
@@ -60,10 +62,6 @@ void report_abi_error(int rc) {
 
 // scratch caches, created on first use and never destroyed (like the reference's planners they are owned by
 // the resource manager, which returns their memory after 5 idle seconds)
-decx::ScratchResource* workspace_cache() {
-    static decx::ScratchResource* r = new decx::ScratchResource(5.0);
-    return r;
-}
 decx::ScratchResource* arena_cache() {
     static decx::ScratchResource* r = new decx::ScratchResource(5.0);
     return r;
@@ -82,33 +80,62 @@ decx::ScratchResource* multi_arena_cache(int device) {          // one per devic
     return r[device & 63];
 }
 
-// one status word per device for the kernels' bounded waits, and a pinned host copy to read it back
-struct StatusWord {
-    struct { void* ptr = nullptr; } dev;   // 4 bytes straight from cudaMalloc: must outlive a release of the pool
+// Status words for the kernels' bounded waits: 64 slots per device (device words straight from cudaMalloc, so they
+// outlive a release of the pool, and a pinned host mirror to read them back).  Every call takes a slot of its own,
+// so calls from several host threads do not share state; a 65th concurrent call waits for a slot.
+struct StatusSlots {
+    unsigned* dev = nullptr;
     unsigned* host = nullptr;
+    uint64_t used = 0;
+    std::mutex mtx;
+    std::condition_variable cv;
 };
-StatusWord* status_word(int device) {
+StatusSlots* status_slots(int device) {
     static std::mutex mtx;
-    static StatusWord words[64];
-    std::lock_guard<std::mutex> lk(mtx);
+    static StatusSlots slots[64];
     if (device < 0 || device >= 64) return nullptr;
-    StatusWord& w = words[device];
-    if (w.dev.ptr == nullptr) {
-        if (cudaMalloc(&w.dev.ptr, sizeof(unsigned)) != cudaSuccess || cudaMemset(w.dev.ptr, 0, sizeof(unsigned)) != cudaSuccess) {
+    StatusSlots& w = slots[device];
+    std::lock_guard<std::mutex> lk(mtx);
+    if (w.dev == nullptr) {
+        void* d = nullptr;
+        if (cudaMalloc(&d, 64 * sizeof(unsigned)) != cudaSuccess || cudaMemset(d, 0, 64 * sizeof(unsigned)) != cudaSuccess) {
             cudaGetLastError();
-            w.dev.ptr = nullptr;
+            if (d != nullptr) cudaFree(d);
             return nullptr;
         }
-        if (cudaHostAlloc(reinterpret_cast<void**>(&w.host), sizeof(unsigned), cudaHostAllocDefault) != cudaSuccess) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&w.host), 64 * sizeof(unsigned), cudaHostAllocDefault) != cudaSuccess) {
             cudaGetLastError();
-            cudaFree(w.dev.ptr);
-            w.dev.ptr = nullptr;
+            cudaFree(d);
             return nullptr;
         }
-        *w.host = 0;
+        std::memset(w.host, 0, 64 * sizeof(unsigned));
+        w.dev = static_cast<unsigned*>(d);
     }
     return &w;
 }
+struct StatusWord {            // one slot, held for the duration of a call
+    StatusSlots* owner = nullptr;
+    int index = -1;
+    unsigned* dev() const { return owner->dev + index; }
+    unsigned* host() const { return owner->host + index; }
+    bool take(int device) {
+        owner = status_slots(device);
+        if (owner == nullptr) return false;
+        std::unique_lock<std::mutex> lk(owner->mtx);
+        owner->cv.wait(lk, [&] { return owner->used != ~0ull; });
+        for (int i = 0; i < 64; ++i)
+            if (!(owner->used >> i & 1ull)) { owner->used |= 1ull << i; index = i; break; }
+        return true;
+    }
+    ~StatusWord() {
+        if (owner == nullptr || index < 0) return;
+        {
+            std::lock_guard<std::mutex> lk(owner->mtx);
+            owner->used &= ~(1ull << index);
+        }
+        owner->cv.notify_one();
+    }
+};
 
 struct DeviceScope {   // makes `device` current for the call, restores the caller's device afterwards
     int prev = 0;
@@ -157,38 +184,38 @@ void gemm_device(de::GPU_Matrix& A_, de::GPU_Matrix& B_, de::GPU_Matrix* C_, de:
     }
     const uint32_t M = A->Height(), N = B->Width(), K = A->Width();
     dst->re_construct(A->Type(), N, M, S);
-    StatusWord* sw = status_word(A->_device);
-    if (!dst->_init || sw == nullptr) {
+    StatusWord sw;
+    if (!dst->_init || !sw.take(A->_device)) {
         S->detach();
         E->detach();
         return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
     }
+    // scratch of THIS call, from the device pool (carved out of chunks the pool already holds after the first
+    // calls): concurrent calls from several host threads each have their own and run on their own streams
     const size_t need = decxb200_gemm_workspace_bytes(dt, M, N, K);
-    void* ws = nullptr;
-    if (need) {
-        ws = workspace_cache()->lock(need, A->_device);
-        if (ws == nullptr) {
-            S->detach();
-            E->detach();
-            return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
-        }
+    decx::PtrInfo<void> ws;
+    if (need && decx::alloc::_device_malloc(&ws, need) != 0) {
+        cudaGetLastError();
+        S->detach();
+        E->detach();
+        return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
     }
     const int rc = decxb200_gemm(dt, S->get_raw_stream_ref(), M, N, K, A->Mat.ptr, A->Pitch(), B->Mat.ptr, B->Pitch(),
                                  C ? C->Mat.ptr : nullptr, C ? C->Pitch() : 0, dst->Mat.ptr, dst->Pitch(), C ? &a : nullptr,
-                                 C ? &b : nullptr, ws, need, static_cast<unsigned*>(sw->dev.ptr));
+                                 C ? &b : nullptr, ws.ptr, need, sw.dev());
     if (rc == 0)
-        cudaMemcpyAsync(sw->host, sw->dev.ptr, sizeof(unsigned), cudaMemcpyDeviceToHost, S->get_raw_stream_ref());
+        cudaMemcpyAsync(sw.host(), sw.dev(), sizeof(unsigned), cudaMemcpyDeviceToHost, S->get_raw_stream_ref());
     E->event_record(S);
     E->synchronize();                       // the API is synchronous, as in the reference (GEMM_LS.cu:102-103)
-    if (need) workspace_cache()->unlock();
+    decx::alloc::_device_dealloc(&ws);
     S->detach();
     E->detach();
     if (rc != 0) return report_abi_error(rc);
-    if (*sw->host != 0) {
+    if (*sw.host() != 0) {
         char msg[96];
-        snprintf(msg, sizeof(msg), "error: a bounded wait inside the GEMM kernel expired (code 0x%x)", *sw->host);
-        *sw->host = 0;
-        cudaMemset(sw->dev.ptr, 0, sizeof(unsigned));
+        snprintf(msg, sizeof(msg), "error: a bounded wait inside the GEMM kernel expired (code 0x%x)", *sw.host());
+        *sw.host() = 0;
+        cudaMemset(sw.dev(), 0, sizeof(unsigned));
         return fail(de::DECX_FAIL_CUDA_STREAM, msg);
     }
 }
@@ -250,10 +277,11 @@ void gemm_host(de::Matrix& A_, de::Matrix& B_, de::Matrix* C_, de::Matrix& dst_)
             cudaGetLastError();                                   // not enough memory somewhere: one GPU does it
         }
     }
-    StatusWord* sw = status_word(device);
+    StatusWord sw;
+    const bool have_sw = sw.take(device);
     const size_t need = decxb200_gemm_host_arena_bytes(dt, M, N, K, C ? 1 : 0);
     void* arena = arena_cache()->lock(need, device);
-    if (arena == nullptr || sw == nullptr) {
+    if (arena == nullptr || !have_sw) {
         if (arena != nullptr) arena_cache()->unlock();
         return fail(de::DECX_FAIL_CUDA_ALLOCATION, "error: Fail to allocate memory on device");
     }
@@ -262,10 +290,10 @@ void gemm_host(de::Matrix& A_, de::Matrix& B_, de::Matrix* C_, de::Matrix& dst_)
     else { one.f[0] = 1.f; one.f[1] = 0.f; }
     const int rc = decxb200_gemm_host(dt, M, N, K, A->data, A->Pitch(), B->data, B->Pitch(), C ? C->data : nullptr,
                                       C ? C->Pitch() : 0, dst->data, dst->Pitch(), C ? &one : nullptr, C ? &one : nullptr,
-                                      arena, need, static_cast<unsigned*>(sw->dev.ptr));
+                                      arena, need, sw.dev());
     arena_cache()->unlock();
     if (rc == DECXB200_EKERNEL) {
-        cudaMemset(sw->dev.ptr, 0, sizeof(unsigned));
+        cudaMemset(sw.dev(), 0, sizeof(unsigned));
         return fail(de::DECX_FAIL_CUDA_STREAM, decxb200_strerror(rc));
     }
     if (rc != 0) return report_abi_error(rc);

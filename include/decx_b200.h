@@ -317,6 +317,13 @@ DECXB200_API int decxb200_last_kernel_variant(void);
  * calling thread's counts of look-ups served from the cache and of fresh cuTensorMapEncodeTiled calls. */
 DECXB200_API void decxb200_tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
 
+/* Tuning aid.  With DECXB200_STATS=1 in the environment the GEMM kernels of the current device add to a 32-word
+ * timing record (ns of the GPU's global timer): [18] / [19] time and count of loader waits for panel flags,
+ * [20] time the MMA-issuing threads waited for operands, [21] for a free accumulator, [22] their whole tile
+ * loops, [23] how many of them were counted.  This call copies the record out (after the kernels launched so far
+ * have finished) and clears it. */
+DECXB200_API int decxb200_debug_stats(unsigned long long out[32]);
+
 /* Static description of an error code returned by this library. */
 DECXB200_API const char* decxb200_strerror(int code);
 

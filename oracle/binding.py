@@ -18,8 +18,15 @@ REF_SO = os.path.join(HERE, "_ref", "libdecx_ref_cpu.so")
 FP32, FP16, CPLXF = 1, 3, 5
 
 
-def build(ref_root="/root/reference"):
+def default_ref_root():
+    """Where the reference's sources are looked for: $DECX_REF_ROOT, else a checkout named `reference` beside this
+    repository."""
+    return os.environ.get("DECX_REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root=None):
     """Compile the C restatement; compile the reference's CPU GEMM too when its sources are present."""
+    ref_root = ref_root or default_ref_root()
     subprocess.run(["make", "-C", HERE, "liboracle.so"], check=True, stdout=subprocess.DEVNULL)
     if os.path.isdir(os.path.join(ref_root, "srcs")):
         subprocess.run(["make", "-C", HERE, "ref", f"REF={ref_root}"], check=True, stdout=subprocess.DEVNULL)

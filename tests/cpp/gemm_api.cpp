@@ -7,6 +7,7 @@
 #include <complex>
 #include <cstdio>
 #include <cstdlib>
+#include <thread>
 #include <vector>
 
 #include "DECX.h"
@@ -366,6 +367,50 @@ static void multi_gpu_host_case() {
     unsetenv("DECX_B200_MULTI_MIN_FLOPS");
 }
 
+// Four host threads multiply different shapes and types at once: each call has its own stream, scratch and
+// status word, so they overlap on the GPU and none may disturb another's result.
+static void concurrent_calls() {
+    struct Job { uint32_t M, N, K; bool half; };
+    const Job jobs[4] = {{700, 300, 520, false}, {257, 1031, 129, false}, {900, 520, 256, true}, {1300, 136, 700, false}};
+    std::vector<double> worst(4, 1e9);
+    std::vector<std::thread> th;
+    for (int t = 0; t < 4; ++t)
+        th.emplace_back([&, t] {
+            const Job j = jobs[t];
+            const de::_DATA_TYPES_FLAGS_ ty = j.half ? de::_FP16_ : de::_FP32_;
+            de::Matrix& A = de::CreateMatrixRef(ty, j.K, j.M);
+            de::Matrix& B = de::CreateMatrixRef(ty, j.N, j.K);
+            de::Matrix& D = de::CreateMatrixRef(ty, j.N, j.M);
+            uint32_t seed = 77 + t;
+            auto r = [&] { seed = seed * 1664525u + 1013904223u; return float(int32_t(seed >> 8) - (1 << 23)) / float(1 << 23); };
+            for (uint32_t i = 0; i < j.M; ++i) for (uint32_t k = 0; k < j.K; ++k) { if (j.half) *A.ptr<de::Half>(i, k) = de::Float2Half(r() * 0.3f); else *A.ptr<float>(i, k) = r(); }
+            for (uint32_t k = 0; k < j.K; ++k) for (uint32_t c = 0; c < j.N; ++c) { if (j.half) *B.ptr<de::Half>(k, c) = de::Float2Half(r() * 0.3f); else *B.ptr<float>(k, c) = r(); }
+            de::GPU_Matrix& dA = de::CreateGPUMatrixRef(ty, j.K, j.M);
+            de::GPU_Matrix& dB = de::CreateGPUMatrixRef(ty, j.N, j.K);
+            de::GPU_Matrix& dD = de::CreateGPUMatrixRef();
+            de::Memcpy(A, dA, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(j.K, j.M), de::DECX_MEMCPY_H2D);
+            de::Memcpy(B, dB, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(j.N, j.K), de::DECX_MEMCPY_H2D);
+            for (int rep = 0; rep < 8; ++rep) de::blas::cuda::GEMM(dA, dB, dD);
+            de::Memcpy(D, dD, de::Point2D(0, 0), de::Point2D(0, 0), de::Point2D(j.N, j.M), de::DECX_MEMCPY_D2H);
+            double w = 0;
+            for (uint32_t i = 0; i < j.M; i += 7)
+                for (uint32_t c = 0; c < j.N; c += 5) {
+                    double s = 0, na = 0, nb = 0;
+                    for (uint32_t k = 0; k < j.K; ++k) {
+                        const double a = j.half ? de::Half2Float(*A.ptr<de::Half>(i, k)) : *A.ptr<float>(i, k);
+                        const double b = j.half ? de::Half2Float(*B.ptr<de::Half>(k, c)) : *B.ptr<float>(k, c);
+                        s += a * b; na += a * a; nb += b * b;
+                    }
+                    const double got = j.half ? de::Half2Float(*D.ptr<de::Half>(i, c)) : *D.ptr<float>(i, c);
+                    w = std::fmax(w, std::fabs(got - s) / std::sqrt(na * nb));
+                }
+            worst[t] = w / (j.half ? 1e-2 : 1e-5);
+            dA.release(); dB.release(); dD.release();
+        });
+    for (auto& t : th) t.join();
+    for (int t = 0; t < 4; ++t) CHECK(worst[t] <= 1.0);
+}
+
 int main() {
     de::InitCPUInfo();
     de::InitCuda();
@@ -388,6 +433,7 @@ int main() {
     gemv_cases();
     transpose_cast_cases();
     multi_gpu_host_case();
+    concurrent_calls();
     sample_known_answer();
     error_paths();
     de::cuda::DECX_CUDA_exit();

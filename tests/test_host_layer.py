@@ -79,7 +79,7 @@ def test_host_units_under_sanitizers(tmp_path, san):
     assert "ERROR: AddressSanitizer" not in r.stderr and "runtime error:" not in r.stderr and "WARNING: ThreadSanitizer" not in r.stderr
 
 
-REF_INC = os.path.join(os.environ.get("DECX_REF_ROOT", "/root/reference"), "srcs", "includes")
+REF_INC = os.path.join(os.environ.get("DECX_REF_ROOT") or os.path.join(os.path.dirname(ROOT), "reference"), "srcs", "includes")
 
 
 @pytest.mark.skipif(not os.path.isdir(REF_INC), reason="reference headers not mounted")
