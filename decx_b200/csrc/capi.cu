@@ -879,6 +879,7 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
     f.pitch = ldb * 2;
     f.arrived = reinterpret_cast<unsigned*>(sc);
     f.published = reinterpret_cast<unsigned*>(sc + 64);
+    f.next_batch = reinterpret_cast<unsigned*>(sc + 128);
     f.ready_flags = ready_flags;
     f.pub_flags = pub_flags;
     f.epoch = epoch;

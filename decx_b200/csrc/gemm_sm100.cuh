@@ -137,6 +137,7 @@ struct FetchParams {
     uint64_t pitch;            // bytes per row, source and destination
     unsigned* arrived;         // [MAX_PANELS] batches stored so far, zero at launch
     unsigned* published;       // [MAX_PANELS] batches of publishing jobs stored so far, zero at launch
+    unsigned* next_batch;      // the next batch nobody has taken yet, zero at launch
     unsigned* ready_flags;     // [MAX_PANELS] <- epoch when every batch of the panel is stored (= GemmParams::panel_flags)
     unsigned* pub_flags;       // [MAX_PANELS] <- epoch when every publishing batch of the panel is stored
     unsigned epoch;
@@ -386,58 +387,87 @@ __device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmPara
     __syncwarp();
 }
 
-__device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParams& p, uint32_t courier,
-                                           uint32_t n_couriers, uint32_t lane) {
-    uint32_t job = 0, job_first = 0;             // first batch index of `job`
+// One courier (a warp).  Batches are handed out by a global counter (f.next_batch), so every batch before the one a
+// courier holds has been taken by somebody: the list is worked through in order whatever the couriers' speeds.
+// `step` advances by at most one batch and never blocks for long when `may_block` is false -- that is what lets the
+// epilogue warps, idle for most of a 256 x 512 tile, carry batches between two accumulator drains.
+struct Courier {
+    uint32_t job = 0, job_first = 0;             // current job and its first batch index
     uint32_t spr = 0, nseg = 0, nb = 0;
     FetchJob J;
-    bool have = false, gate_open = false;
+    bool have = false, gate_open = false, done = false, holding = false;
+    uint32_t cur = 0;                            // batch taken from the counter and not yet copied (if `holding`)
     uint32_t pend_panel = 0, pend_pub = 0, pend = 0;      // batches copied but not yet counted
-    for (uint32_t b = courier; b < f.total_batches; b += n_couriers) {
-        for (;;) {                               // the job that holds batch b (batches only move forward)
-            if (!have) {
-                if (job >= f.n_jobs) {           // inconsistent table: stop rather than read past it
-                    fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
-                    return;
-                }
-                J = f.jobs[job];
-                spr = (J.bytes + 511u) / 512u;
-                nseg = J.rows * spr;
-                nb = fetch_job_batches(J.rows, J.bytes);
-                have = true;
-                gate_open = (J.gate == nullptr);
+    uint64_t gate_t0 = 0;
+
+    __device__ __forceinline__ void flush(const FetchParams& f, const GemmParams& p, uint32_t lane) {
+        fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
+        pend = 0;
+    }
+
+    __device__ __forceinline__ void step(const FetchParams& f, const GemmParams& p, uint32_t lane, bool may_block) {
+        if (done) return;
+        if (!holding) {
+            uint32_t b = 0;
+            if (lane == 0) b = atomicAdd(f.next_batch, 1u);
+            b = __shfl_sync(0xffffffffu, b, 0);
+            if (b >= f.total_batches) {
+                flush(f, p, lane);
+                done = true;
+                return;
             }
-            if (b < job_first + nb) break;
-            job_first += nb;
-            ++job;
-            have = false;
-        }
-        if (J.panel != pend_panel || J.publish != pend_pub) {
-            fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
-            pend_panel = J.panel;
-            pend_pub = J.publish;
-            pend = 0;
+            cur = b;
+            holding = true;
+            for (;;) {                           // the job that holds batch `cur` (batches only move forward)
+                if (!have) {
+                    if (job >= f.n_jobs) {       // inconsistent table: stop rather than read past it
+                        flush(f, p, lane);
+                        done = true;
+                        return;
+                    }
+                    J = f.jobs[job];
+                    spr = (J.bytes + 511u) / 512u;
+                    nseg = J.rows * spr;
+                    nb = fetch_job_batches(J.rows, J.bytes);
+                    have = true;
+                    gate_open = (J.gate == nullptr);
+                    gate_t0 = 0;
+                }
+                if (cur < job_first + nb) break;
+                job_first += nb;
+                ++job;
+                have = false;
+            }
+            if (J.panel != pend_panel || J.publish != pend_pub) {
+                flush(f, p, lane);               // hands in published batches BEFORE any wait on another GPU's flag
+                pend_panel = J.panel;
+                pend_pub = J.publish;
+            }
         }
         if (!gate_open) {
-            // the piece is being produced elsewhere (another GPU's couriers or a copy engine): wait for its flag
-            uint32_t ok = 1;
+            // the piece is being produced elsewhere (another GPU's couriers or a copy engine): look at its flag
+            uint32_t state = 0;                  // 0 closed, 1 open, 2 timed out
             if (lane == 0) {
-                const uint64_t t0 = global_timer_ns();
-                while (int(ld_acquire_sys(J.gate) - f.epoch) < 0) {
-                    if (global_timer_ns() - t0 > p.wait_limit_ns) { ok = 0; break; }
+                if (gate_t0 == 0) gate_t0 = global_timer_ns();
+                for (;;) {
+                    if (int(ld_acquire_sys(J.gate) - f.epoch) >= 0) { state = 1; break; }
+                    if (global_timer_ns() - gate_t0 > p.wait_limit_ns) { state = 2; break; }
+                    if (!may_block) break;
                     __nanosleep(256);
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
+            state = __shfl_sync(0xffffffffu, state, 0);
+            if (state == 2) {
                 if (lane == 0) report(p, KS_TIMEOUT_FETCH);
-                fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
+                flush(f, p, lane);
+                done = true;
                 return;
             }
+            if (state == 0) return;              // not yet: the caller has other things to look at
             (void)ld_acquire_sys(J.gate);        // every lane orders its own loads of the piece after the flag
             gate_open = true;
         }
-        const uint32_t g0 = (b - job_first) * FETCH_UNROLL;
+        const uint32_t g0 = (cur - job_first) * FETCH_UNROLL;
         uint32_t row = g0 / (spr ? spr : 1u), cs = g0 - row * spr;
         uint4 v[FETCH_UNROLL];
         uint64_t off[FETCH_UNROLL];
@@ -453,9 +483,9 @@ __device__ __forceinline__ void fetch_role(const FetchParams& f, const GemmParam
         for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
             if (off[u] != ~0ull) *reinterpret_cast<uint4*>(f.dst + off[u]) = v[u];
         ++pend;
+        holding = false;
     }
-    fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
-}
+};
 
 template <int KIND, int CTAS, int NACC, int FETCH>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH>::THREADS, 1)
@@ -711,7 +741,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
     } else if (FETCH > 0 && warp >= 2u + Cfg::EPI_WARPS) {
         // ------------------------------------------------------------------ couriers (B from the other GPUs)
-        fetch_role(f, p, blockIdx.x * FETCH + (warp - 2u - Cfg::EPI_WARPS), gridDim.x * FETCH, lane);
+        Courier c;
+        while (!c.done) c.step(f, p, lane, true);
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..)
         const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
@@ -740,6 +771,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         const bool ragged_n = ((p.N * ((KIND == 0) ? 2u : 4u)) & 15u) != 0u;
         uint32_t it = 0;                                     // accumulation chains seen so far
         bool ok = true;
+        Courier courier;                                     // used when FETCH > 0: see the wait below
         for (uint32_t t = worker; t < n_tiles && ok; t += n_workers) {
             uint32_t tm, tn;
             tile_coords(t, p, tm, tn);
@@ -811,6 +843,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 // warps 6..9 accumulator 1 of every tile
                 const uint32_t a = (NACC == 2) ? colpart : (it & 1u);
                 const uint32_t aph = (NACC == 2) ? (it & 1u) : ((it >> 1) & 1u);
+                if constexpr (FETCH > 0) {
+                    // this warp has nothing to do until the tile's MMAs are done: carry batches of B meanwhile
+                    while (!courier.done && !mbar_try_wait(accf_bar + 8 * a, aph)) courier.step(f, p, lane, false);
+                    courier.flush(f, p, lane);           // nothing copied stays uncounted while the tile is drained
+                }
                 if (!mbar_wait_bounded(accf_bar + 8 * a, aph, limit)) {
                     if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
                     ok = false;
@@ -868,6 +905,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 }
                 ++it;
             }
+        }
+        if constexpr (FETCH > 0) {
+            // no tiles left (or none at all) for this worker: full-time courier until the list is done
+            while (!courier.done) courier.step(f, p, lane, true);
         }
     }
 
