@@ -23,9 +23,16 @@ class DecxB200Error(RuntimeError):
 
 class FetchJob(ctypes.Structure):
     """``decxb200_fetch_job``: one piece of B a GPU brings into its replica while the GEMM runs."""
-    _fields_ = [("src", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("row0", ctypes.c_uint32),
+    _fields_ = [("src", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("dst", ctypes.c_void_p),
+                ("notify", ctypes.c_void_p), ("row0", ctypes.c_uint32),
                 ("rows", ctypes.c_uint32), ("col0", ctypes.c_uint32), ("cols", ctypes.c_uint32),
                 ("panel", ctypes.c_uint32), ("publish", ctypes.c_uint32)]
+
+
+def fetch_job(src, gate, row0, rows, col0, cols, panel, publish=0, dst=None, notify=None):
+    """A ``decxb200_fetch_job``: pull (dst None) or push (dst = the target GPU's replica, notify = its flag)."""
+    return FetchJob(src=src, gate=gate, dst=dst, notify=notify, row0=row0, rows=rows, col0=col0, cols=cols, panel=panel,
+                    publish=publish)
 
 
 def _load():

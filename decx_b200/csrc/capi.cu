@@ -809,7 +809,10 @@ int decxb200_gemm_fp16_panels(void* stream_, uint32_t M, uint32_t N, uint32_t K,
 
 // scratch layout: [0, 256) batch counters, [256, 512) timing record (32 x u64), [512, ...) job table
 constexpr size_t FETCH_TABLE_OFF = 512;
-size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) { return FETCH_TABLE_OFF + size_t(n_jobs) * sizeof(FetchJob); }
+// ... then one counter per job (push jobs count their batches there)
+size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) {
+    return FETCH_TABLE_OFF + size_t(round_up(uint64_t(n_jobs) * sizeof(FetchJob), 256)) + size_t(round_up(uint64_t(n_jobs) * 4, 256));
+}
 
 int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, void* B,
                              uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
@@ -837,7 +840,11 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
         return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas,
                        ready_flags != nullptr ? &g : nullptr);
     }
-    if (jobs == nullptr || ready_flags == nullptr || pub_flags == nullptr || scratch == nullptr ||
+    bool any_pull = false;
+    if (jobs != nullptr)
+        for (uint32_t i = 0; i < n_jobs; ++i) any_pull = any_pull || jobs[i].dst == nullptr;
+    // a GPU that only pushes (the owner) needs no flags of its own: its tiles read the B it already holds
+    if (jobs == nullptr || (any_pull && (ready_flags == nullptr || pub_flags == nullptr)) || scratch == nullptr ||
         scratch_bytes < decxb200_fetch_scratch_bytes(n_jobs) || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0)
         return DECXB200_EWORKSPACE;
     FetchParams f;
@@ -851,23 +858,32 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
         if (uint64_t(j.row0) + j.rows > K) return DECXB200_EINVAL;
         if (j.rows != 0 && (j.src == nullptr || !aligned16(j.src))) return DECXB200_EINVAL;
         if (j.rows == 0 && j.gate == nullptr) return DECXB200_EINVAL;     // a piece nobody delivers and nobody flags
+        if (j.dst != nullptr && (j.rows == 0 || !aligned16(j.dst) || j.publish)) return DECXB200_EINVAL;
+        if (j.dst == nullptr && j.notify != nullptr) return DECXB200_EINVAL;
         FetchJob& t = table[i];
         t.src = static_cast<const uint8_t*>(j.src);
         t.gate = j.gate;
+        t.dst = static_cast<uint8_t*>(j.dst);
+        t.notify = j.notify;
         t.row0 = j.row0; t.rows = j.rows;
         t.byte0 = j.col0 * 2; t.bytes = j.cols * 2;
         t.panel = j.panel;
         t.publish = j.publish ? 1u : 0u;
         const uint32_t nb = fetch_job_batches(t.rows, t.bytes);
-        f.need[t.panel] += nb;
-        if (t.publish) f.pub_need[t.panel] += nb;
+        if (t.dst == nullptr) {
+            f.need[t.panel] += nb;
+            if (t.publish) f.pub_need[t.panel] += nb;
+        }
         f.total_batches += nb;
     }
-    for (uint32_t i = 0; i < n_panels; ++i)
-        if (f.need[i] == 0) return DECXB200_EINVAL;       // a panel nothing delivers would never be flagged
+    if (any_pull)
+        for (uint32_t i = 0; i < n_panels; ++i)
+            if (f.need[i] == 0) return DECXB200_EINVAL;   // a panel nothing delivers would never be flagged
     uint8_t* sc = static_cast<uint8_t*>(scratch);
     cudaError_t e;
+    const size_t table_bytes = size_t(round_up(uint64_t(n_jobs) * sizeof(FetchJob), 256));
     if ((e = cudaMemsetAsync(sc, 0, FETCH_TABLE_OFF, stream)) != cudaSuccess) return int(e);
+    if ((e = cudaMemsetAsync(sc + FETCH_TABLE_OFF + table_bytes, 0, size_t(n_jobs) * 4, stream)) != cudaSuccess) return int(e);
     // pageable source: staged by the runtime before the call returns, so `table` may go out of scope
     if ((e = cudaMemcpyAsync(sc + FETCH_TABLE_OFF, table.data(), size_t(n_jobs) * sizeof(FetchJob), cudaMemcpyHostToDevice,
                              stream)) != cudaSuccess)
@@ -880,11 +896,12 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
     f.arrived = reinterpret_cast<unsigned*>(sc);
     f.published = reinterpret_cast<unsigned*>(sc + 64);
     f.next_batch = reinterpret_cast<unsigned*>(sc + 128);
+    f.job_done = reinterpret_cast<unsigned*>(sc + FETCH_TABLE_OFF + table_bytes);
     f.ready_flags = ready_flags;
     f.pub_flags = pub_flags;
     f.epoch = epoch;
-    return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas, &g,
-                   &f);
+    return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas,
+                   any_pull ? &g : nullptr, &f);
 }
 
 int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes,

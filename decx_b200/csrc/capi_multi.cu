@@ -263,12 +263,12 @@ int decxb200_gemm_host_multi(int dtype, int n_devices, const int* devices, uint3
                     for (uint32_t p = 0; p < pl.n_panels; ++p) {
                         const uint32_t w = pl.panel_end[p] - c0;
                         // my own rows arrive by copy engine: wait for their flag, nothing to copy
-                        jobs.push_back({nullptr, flags(d) + 16 + p, gather ? pl.piece0[d] : 0u, 0u, c0, w, p, 0u});
+                        jobs.push_back({nullptr, flags(d) + 16 + p, nullptr, nullptr, gather ? pl.piece0[d] : 0u, 0u, c0, w, p, 0u});
                         if (gather)
                             for (int k = 1; k < n_devices; ++k) {
                                 const int h = (d + k) % n_devices;                                   // stagger the sources
                                 if (pl.nrows[h] == 0 || pl.piece_rows[h] == 0) continue;
-                                jobs.push_back({at(h, pl.off_b), flags(h) + 16 + p, pl.piece0[h], pl.piece_rows[h], c0, w, p, 0u});
+                                jobs.push_back({at(h, pl.off_b), flags(h) + 16 + p, nullptr, nullptr, pl.piece0[h], pl.piece_rows[h], c0, w, p, 0u});
                             }
                         c0 = pl.panel_end[p];
                     }

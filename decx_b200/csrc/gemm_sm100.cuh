@@ -113,16 +113,24 @@ struct GemmParams {
     unsigned long long* stats;
 };
 
-// One piece of B a courier warp copies into this GPU's replica: rows [row0, row0 + rows) x bytes [byte0, byte0 +
-// bytes) of every row, from `src` (same row pitch as the replica; usually another GPU's memory).  rows == 0 is a
-// piece something else delivers (a copy engine): the courier only waits for its gate and counts it.
+// One piece of B a courier warp copies: rows [row0, row0 + rows) x bytes [byte0, byte0 + bytes) of every row, from
+// `src` to `dst` (both laid out like the replica, same row pitch).  Two directions:
+//   pull  (dst == nullptr: this GPU's replica; src usually another GPU's memory): the piece counts towards the
+//         panel's "complete here" flag; with `publish` it also counts towards this GPU's publish flag.
+//   push  (dst = another GPU's replica, src local): when the whole job is stored, `notify` -- a word in the TARGET's
+//         memory, its publish flag for the panel -- is set to the epoch.  Stores over NVLink are posted: no
+//         request has to travel towards the sender, whose inbound link may be busy receiving D.
+// rows == 0 is a piece something else delivers (a pushing GPU, a copy engine): the courier only waits for its gate
+// and counts it.
 struct FetchJob {
     const uint8_t* src;
     const unsigned* gate;      // word that must have reached `epoch` before src may be read; nullptr: readable now
+    uint8_t* dst;              // nullptr: the local replica
+    unsigned* notify;          // push jobs: word (in the target's memory) to set when the job is complete
     uint32_t row0, rows;
     uint32_t byte0, bytes;     // bytes % 16 == 0
     uint32_t panel;            // column panel the piece belongs to
-    uint32_t publish;          // 1: other GPUs fetch this piece from here once it has landed (pub_flags)
+    uint32_t publish;          // pull jobs: 1 = other GPUs fetch this piece from here once it has landed (pub_flags)
 };
 constexpr uint32_t FETCH_UNROLL = 16;                   // 512-byte segments per batch (one warp, one go): 8 KB
 __host__ __device__ inline uint32_t fetch_job_batches(uint32_t rows, uint32_t bytes) {
@@ -138,6 +146,7 @@ struct FetchParams {
     unsigned* arrived;         // [MAX_PANELS] batches stored so far, zero at launch
     unsigned* published;       // [MAX_PANELS] batches of publishing jobs stored so far, zero at launch
     unsigned* next_batch;      // the next batch nobody has taken yet, zero at launch
+    unsigned* job_done;        // [n_jobs] batches stored per job (push jobs), zero at launch
     unsigned* ready_flags;     // [MAX_PANELS] <- epoch when every batch of the panel is stored (= GemmParams::panel_flags)
     unsigned* pub_flags;       // [MAX_PANELS] <- epoch when every publishing batch of the panel is stored
     unsigned epoch;
@@ -366,22 +375,30 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
 // (panel, publishing or not) group of jobs, or runs out of work -- one fence per group instead of one per 8 KB.
 // (A system-scope fence per batch limited the copy to ~130 GB/s.)  The publishing job of a panel comes first in
 // the list, so a courier always hands in its published batches BEFORE it starts waiting on another GPU's flag.
-__device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmParams& p, uint32_t lane, uint32_t panel,
-                                            uint32_t publish, uint32_t count) {
+__device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmParams& p, uint32_t lane, const FetchJob& J,
+                                            uint32_t job, uint32_t job_batches, uint32_t count) {
     if (count == 0) return;
+    const bool push = J.dst != nullptr;
     // the stores of every lane are performed before the counts below can be seen to include these batches:
-    // readers of pub_flags are other GPUs (system scope), readers of ready_flags are this GPU's loaders
-    if (publish) __threadfence_system(); else __threadfence();
+    // readers of publish / notify flags are other GPUs (system scope), readers of ready_flags this GPU's loaders
+    if (push || J.publish) __threadfence_system(); else __threadfence();
     __syncwarp();
     if (lane == 0) {
-        if (publish && atomicAdd(f.published + panel, count) + count == f.pub_need[panel]) {
-            __threadfence_system();
-            st_release_sys(f.pub_flags + panel, f.epoch);
-        }
-        if (atomicAdd(f.arrived + panel, count) + count == f.need[panel]) {
-            __threadfence();
-            st_release_sys(f.ready_flags + panel, f.epoch);
-            if (p.stats != nullptr) p.stats[panel] = global_timer_ns();
+        if (push) {
+            if (J.notify != nullptr && atomicAdd(f.job_done + job, count) + count == job_batches) {
+                __threadfence_system();
+                st_release_sys(J.notify, f.epoch);
+            }
+        } else {
+            if (J.publish && atomicAdd(f.published + J.panel, count) + count == f.pub_need[J.panel]) {
+                __threadfence_system();
+                st_release_sys(f.pub_flags + J.panel, f.epoch);
+            }
+            if (atomicAdd(f.arrived + J.panel, count) + count == f.need[J.panel]) {
+                __threadfence();
+                st_release_sys(f.ready_flags + J.panel, f.epoch);
+                if (p.stats != nullptr) p.stats[J.panel] = global_timer_ns();
+            }
         }
     }
     __syncwarp();
@@ -397,11 +414,13 @@ struct Courier {
     FetchJob J;
     bool have = false, gate_open = false, done = false, holding = false;
     uint32_t cur = 0;                            // batch taken from the counter and not yet copied (if `holding`)
-    uint32_t pend_panel = 0, pend_pub = 0, pend = 0;      // batches copied but not yet counted
+    uint32_t pend = 0;                           // batches of job PJ copied but not yet counted
+    FetchJob PJ;
+    uint32_t pend_job = 0, pend_nb = 0;
     uint64_t gate_t0 = 0;
 
     __device__ __forceinline__ void flush(const FetchParams& f, const GemmParams& p, uint32_t lane) {
-        fetch_flush(f, p, lane, pend_panel, pend_pub, pend);
+        fetch_flush(f, p, lane, PJ, pend_job, pend_nb, pend);
         pend = 0;
     }
 
@@ -438,11 +457,10 @@ struct Courier {
                 ++job;
                 have = false;
             }
-            if (J.panel != pend_panel || J.publish != pend_pub) {
-                flush(f, p, lane);               // hands in published batches BEFORE any wait on another GPU's flag
-                pend_panel = J.panel;
-                pend_pub = J.publish;
-            }
+            if (pend != 0 && job != pend_job) flush(f, p, lane);   // hands a job's batches in BEFORE any wait on a flag
+            PJ = J;
+            pend_job = job;
+            pend_nb = nb;
         }
         if (!gate_open) {
             // the piece is being produced elsewhere (another GPU's couriers or a copy engine): look at its flag
@@ -479,9 +497,10 @@ struct Courier {
             if (valid) v[u] = ld_volatile_v4(J.src + off[u]);
             if (++cs == spr) { cs = 0; ++row; }
         }
+        uint8_t* const dst = J.dst != nullptr ? J.dst : f.dst;
 #pragma unroll
         for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
-            if (off[u] != ~0ull) *reinterpret_cast<uint4*>(f.dst + off[u]) = v[u];
+            if (off[u] != ~0ull) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
         ++pend;
         holding = false;
     }

@@ -2,9 +2,50 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cstdio>
+#include <cstdlib>
+#if defined(__linux__)
+#include <sys/syscall.h>
+#include <unistd.h>
+#endif
+
 #include "internal.h"
 
 // ------------------------------------------------------------------------------------------------ host matrix
+namespace {
+// Host matrices of 64 MiB and more get their pages interleaved over the NUMA nodes of the machine (mbind,
+// MPOL_INTERLEAVE, before the first touch).  A matrix that one thread allocates and zero-fills would otherwise live
+// on that thread's node alone, and every GPU behind the other socket would pull its rows across the inter-socket
+// link: with eight GPUs moving their row blocks at once that link, not PCIe, set the pace of the host-matrix GEMM.
+// Best effort: any failure leaves the default placement.
+void interleave_pages(void* addr, uint64_t bytes) {
+#if defined(__linux__) && defined(SYS_mbind)
+    unsigned long mask = 0;
+    if (FILE* f = std::fopen("/sys/devices/system/node/online", "r")) {
+        char buf[128] = {0};
+        if (std::fgets(buf, sizeof(buf), f) != nullptr) {
+            for (const char* p = buf; *p != '\0' && *p != '\n';) {          // "0-1", "0,2-3", ...
+                char* end = nullptr;
+                const long a = std::strtol(p, &end, 10);
+                if (end == p) break;
+                long b = a;
+                p = end;
+                if (*p == '-') { b = std::strtol(p + 1, &end, 10); p = end; }
+                for (long n = a; n <= b && n < 64; ++n) mask |= 1ul << n;
+                if (*p == ',') ++p;
+            }
+        }
+        std::fclose(f);
+    }
+    if ((mask & (mask - 1)) == 0) return;                                  // one node (or none known): nothing to spread
+    const int MPOL_INTERLEAVE_ = 3;
+    syscall(SYS_mbind, addr, static_cast<unsigned long>(bytes), MPOL_INTERLEAVE_, &mask, 65ul, 0u);
+#else
+    (void)addr; (void)bytes;
+#endif
+}
+}  // namespace
+
 namespace {
 void fill_layout(de::MatrixLayout& l, de::_DATA_TYPES_FLAGS_ t, uint32_t w, uint32_t h, uint32_t align_bytes) {
     l._single_element_size = decx::element_size(t);
@@ -34,11 +75,13 @@ void decx::_Matrix::construct(const de::_DATA_TYPES_FLAGS_ t, uint32_t width, ui
     total_bytes = uint64_t(_layout.pitch) * height * _layout._single_element_size;
     if (total_bytes == 0) return;
     const uint64_t padded = (total_bytes + 63) / 64 * 64;
-    data = std::aligned_alloc(64, padded);
+    // large matrices are page-aligned so that their pages can be spread over the NUMA nodes before first touch
+    data = std::aligned_alloc(padded >= (64u << 20) ? 4096 : 64, padded >= (64u << 20) ? (padded + 4095) / 4096 * 4096 : padded);
     if (data == nullptr) {
         decx::err::set(de::GetLastError(), de::DECX_FAIL_ALLOCATION, "error: Fail to allocate memory on RAM");
         return;
     }
+    if (padded >= (64u << 20)) interleave_pages(data, (padded + 4095) / 4096 * 4096);
     std::memset(data, 0, padded);
     _shared = new int(1);
     _owner = true;

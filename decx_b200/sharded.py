@@ -33,9 +33,11 @@ at a panel boundary, and the 256 x 512 tile applies.
 
 "fused" overlap (the default for fp16 on GPUs) goes one step further and needs no copy engine, no communication
 stream and no NCCL call inside the step: the GEMM kernel itself brings B in (decxb200_gemm_fp16_fetch).  Every
-CTA carries two courier warps; together they copy this rank's row piece of each panel from the owner's B
-(scatter: the owner sends every byte once), publish it through a flag in symmetric memory, and copy the other
-pieces from the ranks that hold them (all-gather), panel by panel, with 16-byte peer loads.  The tiles of a panel
+CTA carries two courier warps, and its epilogue warps join in while their tile is being multiplied.  The OWNER's
+couriers push one row piece of each panel into every other rank's replica and raise that rank's publish flag
+(scatter: the owner sends every byte once, with posted stores); the other ranks' couriers wait for their own
+piece and copy the remaining pieces from the ranks that hold them (all-gather), panel by panel, with 16-byte
+peer loads.  The tiles of a panel
 start when its pieces are counted complete.  One launch per rank does broadcast, product and -- through D in
 the owner's memory -- the gather; two stream-ordered symmetric-memory barriers bracket it.
 
@@ -129,27 +131,47 @@ def row_pieces(K, parts, align=16):
     return out
 
 
-def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr):
-    """Job list of `rank` for the fused kernel, as tuples (src, gate, row0, rows, col0, cols, panel, publish).
+def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr, scatter="push"):
+    """Job list of `rank` for the fused kernel, as tuples
+    (src, gate, row0, rows, col0, cols, panel, publish, dst, notify).
 
-    `active` are the ranks that run a kernel (they have rows of A); the non-owners among them each take one row
-    piece of every panel from the owner (published to the others) and the remaining pieces from each other.
+    `active` are the ranks that run a kernel (they have rows of A).  The non-owners among them ("holders") each
+    become the first holder of one row piece of every panel and fetch the remaining pieces from each other, gated
+    on the holder's publish flag for the panel.  How a holder gets its own piece:
+      scatter="push" (default): the OWNER's couriers store it into the holder's replica and then set the holder's
+          publish flag (posted stores: no request travels towards the owner, whose inbound link carries D); the
+          holder lists the piece as a rows == 0 job gated on its own flag;
+      scatter="pull": the holder's couriers read it from the owner's B and publish it themselves.
     b_ptr[r] / pub_ptr[r]: address of rank r's replica of B / of its publish flags, as this rank maps them."""
     holders = [r for r in active if r != owner]
-    if rank == owner or rank not in holders:
+    if rank not in active or not holders:
         return []
-    me = holders.index(rank)
     pieces = row_pieces(K, len(holders))
     jobs = []
+    if rank == owner:
+        if scatter != "push":
+            return []
+        for p, (c0, w) in enumerate(panels):
+            for k in range(len(holders)):
+                i = (p + k) % len(holders)                    # start every panel at another target
+                r0, nr = pieces[i]
+                if nr:
+                    q = holders[i]
+                    jobs.append((b_ptr[owner], None, r0, nr, c0, w, p, 0, b_ptr[q], pub_ptr[q] + 4 * p))
+        return jobs
+    me = holders.index(rank)
     for p, (c0, w) in enumerate(panels):
         r0, nr = pieces[me]
         if nr:
-            jobs.append((b_ptr[owner], None, r0, nr, c0, w, p, 1 if len(holders) > 1 else 0))
+            if scatter == "push":
+                jobs.append((None, pub_ptr[rank] + 4 * p, r0, 0, c0, w, p, 0, None, None))
+            else:
+                jobs.append((b_ptr[owner], None, r0, nr, c0, w, p, 1 if len(holders) > 1 else 0, None, None))
         for d in range(1, len(holders)):
             h = (me + d) % len(holders)                       # stagger the sources over the ranks
             r0, nr = pieces[h]
             if nr:
-                jobs.append((b_ptr[holders[h]], pub_ptr[holders[h]] + 4 * p, r0, nr, c0, w, p, 0))
+                jobs.append((b_ptr[holders[h]], pub_ptr[holders[h]] + 4 * p, r0, nr, c0, w, p, 0, None, None))
     return jobs
 
 
@@ -172,7 +194,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None, overlap=None, tile=0):
+                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -182,6 +204,7 @@ class ShardedGemm:
         if not self.on_gpu and gemm_fn is None:
             raise RuntimeError("ShardedGemm computes on CUDA devices only (a host GEMM can only be injected by tests)")
         self.gemm_fn = gemm_fn
+        self._scatter = scatter
         self.bcast = bcast or ("p2p" if self.on_gpu else "broadcast")
         # SMs left free for the communication kernels while a GEMM runs: the GEMM is persistent (one CTA per
         # SM for its whole duration), so without this NCCL's broadcast of the next panel cannot get an SM
@@ -330,8 +353,10 @@ class ShardedGemm:
     def _fused_prepare(self):
         capi = self._capi
         active = [r for r, (_, n) in enumerate(self.rows) if n > 0]
-        tuples = fetch_jobs(self.rank, self.owner, active, self.K, self.panels, self._bptrs, self._pub_ptrs)
-        self._jobs = [capi.FetchJob(*t) for t in tuples]
+        tuples = fetch_jobs(self.rank, self.owner, active, self.K, self.panels, self._bptrs, self._pub_ptrs,
+                            scatter=self._scatter)
+        self._jobs = [capi.fetch_job(*t) for t in tuples]
+        self._pulls = any(t[8] is None for t in tuples)
         need = int(capi.lib.decxb200_fetch_scratch_bytes(max(len(self._jobs), 1)))
         self._fetch_scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
 
@@ -341,10 +366,11 @@ class ShardedGemm:
         G = self._G
         ends = [c0 + w for c0, w in self.panels]
         jobs = self._jobs if fetch else []
-        gated = bool(jobs) or not self.is_owner
+        gated = (bool(jobs) and self._pulls) or not self.is_owner
         with torch.cuda.device(self.device):
             G.gemm_fp16_fetch(self.A, self.Bfull, self._d_ptr, self.N, ends, self.flags if gated else None,
-                              self.pub_flags if jobs else None, epoch, jobs, self._fetch_scratch if jobs else None,
+                              self.pub_flags if (jobs and self._pulls) else None, epoch, jobs,
+                              self._fetch_scratch if jobs else None,
                               status=self.status, max_ctas=self._max_ctas, tile=self._tile)
         self.launches += self._capi.lib.decxb200_last_launch_count()
         self.kernel_variant = self._capi.lib.decxb200_last_kernel_variant()
@@ -352,7 +378,7 @@ class ShardedGemm:
     def fetch_stats(self):
         """Timing record of the last fused launch on this rank (after a synchronize), in microseconds relative
         to the kernel's start: when each panel was complete, kernel duration, total loader wait."""
-        if self.overlap != "fused" or not self._jobs:
+        if self.overlap != "fused" or not self._jobs or not self._pulls:
             return None
         w = self._fetch_scratch[256:512].view(torch.int64).cpu().tolist()
         t0 = w[16]

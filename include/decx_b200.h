@@ -266,6 +266,11 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
  * `gate`.  So the owner sends every byte of B once (scatter) and the GPUs complete each other (all-gather),
  * inside the same launch that multiplies and that stores D into the owner's memory.
  *
+ *   A job may also PUSH: dst names another GPU's replica and src is local; when all of the job is stored, `notify`
+ *   (that GPU's publish flag for the panel) is set.  Posted stores need no request towards the sender, so the
+ *   owner -- whose inbound link is busy receiving D -- scatters B by pushing, and the receivers list the pushed
+ *   piece as a rows == 0 job gated on their own publish flag.  A GPU whose jobs all push (the owner) passes NULL
+ *   for ready_flags / pub_flags and runs ungated.
  *   jobs:      HOST array, copied by the call.  gate == NULL: the source is readable now.  rows == 0: a piece
  *              that something else writes into the replica (a copy engine); the courier only waits for its
  *              gate and counts it.  Every panel needs at least one job.  col0, cols: multiples of 8.
@@ -281,6 +286,8 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
 typedef struct decxb200_fetch_job {
     const void* src;
     const unsigned* gate;
+    void* dst;                 /* NULL: pull into the local replica; else PUSH: the target GPU's replica */
+    unsigned* notify;          /* push jobs: word in the target's memory set to `epoch` when the job is complete */
     uint32_t row0, rows;
     uint32_t col0, cols;
     uint32_t panel;

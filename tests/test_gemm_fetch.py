@@ -41,7 +41,7 @@ def _jobs(capi, src_ptrs, gates, K, ends, pieces, me):
             if nr == 0:
                 continue
             own = h == me
-            jobs.append(capi.FetchJob(src_ptrs[-1] if own else src_ptrs[h], None if own else gates[h] + 4 * p,
+            jobs.append(capi.fetch_job(src_ptrs[-1] if own else src_ptrs[h], None if own else gates[h] + 4 * p,
                                       r0, nr, c0, c1 - c0, p, 1 if own else 0))
         c0 = c1
     return jobs
@@ -106,9 +106,9 @@ def test_fetch_gates_opened_late_and_wait_only_piece(G, dev):
     rows = [(0, 700), (700, 648), (1348, 700)]
     jobs, c0 = [], 0
     for p, c1 in enumerate(ends):
-        jobs.append(capi.FetchJob(gB.view.data_ptr(), None, rows[0][0], rows[0][1], c0, c1 - c0, p, 1))
-        jobs.append(capi.FetchJob(h1.view.data_ptr(), gate1.data_ptr() + 4 * p, rows[1][0], rows[1][1], c0, c1 - c0, p, 0))
-        jobs.append(capi.FetchJob(None, gate2.data_ptr() + 4 * p, rows[2][0], 0, c0, c1 - c0, p, 0))
+        jobs.append(capi.fetch_job(gB.view.data_ptr(), None, rows[0][0], rows[0][1], c0, c1 - c0, p, 1))
+        jobs.append(capi.fetch_job(h1.view.data_ptr(), gate1.data_ptr() + 4 * p, rows[1][0], rows[1][1], c0, c1 - c0, p, 0))
+        jobs.append(capi.fetch_job(None, gate2.data_ptr() + 4 * p, rows[2][0], 0, c0, c1 - c0, p, 0))
         c0 = c1
     scratch = torch.empty(capi.lib.decxb200_fetch_scratch_bytes(len(jobs)), dtype=torch.uint8, device=dev)
     torch.cuda.synchronize()
@@ -145,15 +145,57 @@ def test_fetch_argument_errors(G, dev):
     D = torch.zeros(256, 1024, dtype=torch.float16, device=dev)
     flags = torch.zeros(32, dtype=torch.int32, device=dev)
     scratch = torch.empty(4096, dtype=torch.uint8, device=dev)
-    ok = capi.FetchJob(B.data_ptr(), None, 0, 64, 0, 512, 0, 1)
+    ok = capi.fetch_job(B.data_ptr(), None, 0, 64, 0, 512, 0, 1)
 
     def call(jobs, ends=(512, 1024)):
         G.gemm_fp16_fetch(A, B, D.data_ptr(), 1024, list(ends), flags[:16], flags[16:], 1, jobs, scratch)
 
     for bad in ([ok],                                                            # panel 1 has no job
-                [ok, capi.FetchJob(B.data_ptr(), None, 0, 64, 256, 512, 1, 0)],  # columns outside the panel
-                [ok, capi.FetchJob(B.data_ptr(), None, 32, 64, 512, 512, 1, 0)], # rows beyond K
-                [ok, capi.FetchJob(None, None, 0, 0, 512, 512, 1, 0)]):          # wait-only piece without a gate
+                [ok, capi.fetch_job(B.data_ptr(), None, 0, 64, 256, 512, 1, 0)],  # columns outside the panel
+                [ok, capi.fetch_job(B.data_ptr(), None, 32, 64, 512, 512, 1, 0)], # rows beyond K
+                [ok, capi.fetch_job(None, None, 0, 0, 512, 512, 1, 0)]):          # wait-only piece without a gate
         with pytest.raises(capi.DecxB200Error) as e:
             call(bad)
         assert e.value.code == -1
+
+
+def test_push_jobs_fill_another_replica_and_raise_its_flags(G, dev):
+    """The owner's side of the scatter: while it multiplies with the B it already holds (no gating), its couriers
+    store row pieces of every panel into two other replicas (other GPUs' memory in the real run) and raise the
+    targets' flags when a piece is complete."""
+    from decx_b200 import capi
+    M, N, K, ends = 770, 2104, 520, [512, 1536, 2104]
+    A, B, _ = make_inputs(np.float16, M, N, K, seed=31, dist="small")
+    gA, gB = Guarded(torch, A, dev), Guarded(torch, B, dev)
+    targets = [Guarded(torch, np.zeros_like(B), dev) for _ in range(2)]
+    tflags = torch.zeros((2, 16), dtype=torch.int32, device=dev)
+    gD = Guarded(torch, np.zeros((M, N), np.float16), dev, fill_logical=0)
+    st = G.new_status(dev)
+    pieces = [(0, 272), (272, 248)]
+    jobs, c0 = [], 0
+    for p, c1 in enumerate(ends):
+        for k in range(2):
+            q = (p + k) % 2
+            jobs.append(capi.fetch_job(gB.view.data_ptr(), None, pieces[q][0], pieces[q][1], c0, c1 - c0, p, 0,
+                                       dst=targets[q].view.data_ptr(), notify=tflags[q].data_ptr() + 4 * p))
+        c0 = c1
+    scratch = torch.empty(capi.lib.decxb200_fetch_scratch_bytes(len(jobs)), dtype=torch.uint8, device=dev)
+    G.gemm_fp16_fetch(gA.view, gB.view, gD.view.data_ptr(), gD.pitch, ends, None, None, 4, jobs, scratch, status=st, tile=WIDE)
+    torch.cuda.synchronize()
+    assert capi.lib.decxb200_last_kernel_variant() == 1022 and int(st.item()) == 0
+    for q, t in enumerate(targets):
+        t.check()
+        r0, nr = pieces[q]
+        assert torch.equal(t.view[r0:r0 + nr], gB.view[r0:r0 + nr])          # its piece, every panel
+        other = pieces[1 - q]
+        assert not t.view[other[0]:other[0] + other[1]].any()                # and nothing else
+        assert (tflags[q, :3] == 4).all() and not tflags[q, 3:].any()
+    gB.check()
+    gD.check()
+    plain = G.gemm(gA.view, gB.view, cta_group=WIDE)
+    torch.cuda.synchronize()
+    assert torch.equal(plain, gD.view)
+    # push jobs may not publish, pull jobs may not notify
+    bad = capi.fetch_job(gB.view.data_ptr(), None, 0, 16, 0, 512, 0, 1, dst=targets[0].view.data_ptr())
+    with pytest.raises(capi.DecxB200Error):
+        G.gemm_fp16_fetch(gA.view, gB.view, gD.view.data_ptr(), gD.pitch, ends, None, None, 5, [bad], scratch)

@@ -113,29 +113,55 @@ def test_fetch_jobs_cover_b_exactly_once_and_gate_on_the_publisher():
     from decx_b200.sharded import fetch_jobs, fetch_panel_plan, row_pieces
     K, N = 2053, 2104
     panels = fetch_panel_plan(N)
-    for world, owner, active in ((2, 0, [0, 1]), (4, 0, [0, 1, 2, 3]), (8, 3, list(range(8))), (4, 0, [0, 1, 2])):
-        b_ptr = [1000 * (r + 1) for r in range(world)]
-        pub_ptr = [50 + 1000 * (r + 1) for r in range(world)]
-        published = {}                                                     # (rank, panel) -> rows it publishes
-        for r in range(world):
-            jobs = fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr)
-            if r == owner or r not in active:
-                assert jobs == []
-                continue
-            for p, (c0, w) in enumerate(panels):
-                mine = [j for j in jobs if j[6] == p]
-                assert all(j[4] == c0 and j[5] == w for j in mine)
-                rows = sorted((j[2], j[3]) for j in mine)
-                assert rows[0][0] == 0 and sum(n for _, n in rows) == K    # every row of the panel, once
-                assert all(a[0] + a[1] == b[0] for a, b in zip(rows, rows[1:]))
-                own = [j for j in mine if j[0] == b_ptr[owner]]
-                assert len(own) == 1 and own[0][1] is None                 # one piece straight from the owner
-                published[(r, p)] = (own[0][2], own[0][3])
-                assert mine[0] is own[0] or mine[0] == own[0]              # and it comes first (others wait on it)
-        # a gated job reads exactly the rows its source publishes, behind that source's flag for the panel
-        for r in range(world):
-            for j in fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr):
-                if j[1] is not None:
-                    src_rank = b_ptr.index(j[0])
-                    assert j[1] == pub_ptr[src_rank] + 4 * j[6] and j[7] == 0
-                    assert published[(src_rank, j[6])] == (j[2], j[3])
+    SRC, GATE, R0, NR, C0, W, P, PUB, DST, NOTIFY = range(10)
+    for scatter in ("push", "pull"):
+        for world, owner, active in ((2, 0, [0, 1]), (4, 0, [0, 1, 2, 3]), (8, 3, list(range(8))), (4, 0, [0, 1, 2])):
+            b_ptr = [1000 * (r + 1) for r in range(world)]
+            pub_ptr = [50 + 1000 * (r + 1) for r in range(world)]
+            holders = [r for r in active if r != owner]
+            held = {}                                                          # (rank, panel) -> rows it holds first
+            owner_jobs = fetch_jobs(owner, owner, active, K, panels, b_ptr, pub_ptr, scatter)
+            if scatter == "pull":
+                assert owner_jobs == []
+            else:
+                # the owner pushes every row of every panel exactly once, each piece to one holder, flag = that holder's
+                for p, (c0, w) in enumerate(panels):
+                    mine = [j for j in owner_jobs if j[P] == p]
+                    rows = sorted((j[R0], j[NR]) for j in mine)
+                    assert rows[0][0] == 0 and sum(n for _, n in rows) == K
+                    assert all(a[0] + a[1] == b[0] for a, b in zip(rows, rows[1:]))
+                    assert sorted(b_ptr.index(j[DST]) for j in mine) == sorted(holders)
+                    for j in mine:
+                        q = b_ptr.index(j[DST])
+                        assert j[SRC] == b_ptr[owner] and j[GATE] is None and j[NOTIFY] == pub_ptr[q] + 4 * p
+                        assert (j[C0], j[W]) == (c0, w) and j[PUB] == 0
+                        held[(q, p)] = (j[R0], j[NR])
+            for r in range(world):
+                jobs = fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr, scatter)
+                if r == owner:
+                    continue
+                if r not in active:
+                    assert jobs == []
+                    continue
+                for p, (c0, w) in enumerate(panels):
+                    mine = [j for j in jobs if j[P] == p]
+                    assert all(j[C0] == c0 and j[W] == w and j[DST] is None and j[NOTIFY] is None for j in mine)
+                    own = mine[0]                                              # the own piece comes first
+                    if scatter == "push":
+                        assert own[NR] == 0 and own[GATE] == pub_ptr[r] + 4 * p and held[(r, p)][0] == own[R0]
+                        rows = sorted([held[(r, p)]] + [(j[R0], j[NR]) for j in mine[1:]])
+                    else:
+                        assert own[SRC] == b_ptr[owner] and own[GATE] is None
+                        held[(r, p)] = (own[R0], own[NR])
+                        rows = sorted((j[R0], j[NR]) for j in mine)
+                    assert rows[0][0] == 0 and sum(n for _, n in rows) == K    # every row of the panel, once
+                    assert all(a[0] + a[1] == b[0] for a, b in zip(rows, rows[1:]))
+            # a gated pull reads exactly the rows its source holds first, behind that source's flag for the panel
+            for r in range(world):
+                if r == owner:
+                    continue
+                for j in fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr, scatter):
+                    if j[GATE] is not None and j[NR]:
+                        src_rank = b_ptr.index(j[SRC])
+                        assert j[GATE] == pub_ptr[src_rank] + 4 * j[P] and j[PUB] == 0
+                        assert held[(src_rank, j[P])] == (j[R0], j[NR])
