@@ -581,6 +581,32 @@ def main():
                     G.gemm_host(hA, hB, out=hD, arena=arena, status=st, device=device)
                 e2e["c_abi_ms_per_step"] = (time.perf_counter() - t0e) / 3 * 1e3
                 del hD, arena
+            if world > 1:
+                # what the box gives when every GPU copies at once (one 256 MiB block of A each, then of D back):
+                # the ceiling of any host-matrix path on this machine, beside the single-link figure
+                blk = 256 << 20
+                flat = torch.from_numpy(mA.array).view(torch.uint8).view(-1)
+                bufs = [torch.empty(blk, dtype=torch.uint8, device=torch.device("cuda", d)) for d in range(world)]
+                def timed(devs, to_host):
+                    for d in devs:
+                        torch.cuda.synchronize(d)
+                    t0p = time.perf_counter()
+                    for d in devs:
+                        with torch.cuda.device(d):
+                            if to_host:
+                                flat[d * blk:(d + 1) * blk].copy_(bufs[d], non_blocking=True)
+                            else:
+                                bufs[d].copy_(flat[d * blk:(d + 1) * blk], non_blocking=True)
+                    for d in devs:
+                        torch.cuda.synchronize(d)
+                    return len(devs) * blk / (time.perf_counter() - t0p) / 1e9
+                every = list(range(world))
+                timed(every, False)
+                e2e["pcie"] = {"h2d_one_gpu_gbs": timed([0], False), "h2d_all_gpus_gbs": timed(every, False),
+                               "d2h_one_gpu_gbs": timed([0], True), "d2h_all_gpus_gbs": timed(every, True),
+                               "what": f"256 MiB per GPU, pinned host memory, {world} GPUs at once vs GPU 0 alone"}
+                del bufs
+                vA[:blk // (2 * K) + 1].copy_(sg.A[:blk // (2 * K) + 1]) if sg.nrows else None
             for m in (mA, mB, mD):
                 m.release()
             if not e2e["parity"]["ok"]:

@@ -44,7 +44,7 @@ GemvPlan plan_gemv(int dtype, int accu, int trans, uint32_t rows, uint32_t cols)
         g.slice_len = uint32_t(round_up((uint64_t(cols) + want - 1) / want, unit));
     } else {
         const uint32_t col_blocks = (cols + 32 * vec - 1) / (32 * vec);
-        if (col_blocks < 592) want = (592 + col_blocks - 1) / col_blocks;
+        if (col_blocks < 1776) want = (1776 + col_blocks - 1) / col_blocks;      // about 12 CTAs per SM
         const uint32_t unit = GEMV_WARPS * GEMV_UNROLL * 4;            // rows: a few unrolled rounds per warp
         const uint32_t max_slices = (rows + unit - 1) / unit;
         if (want > max_slices) want = max_slices;
