@@ -606,7 +606,6 @@ def main():
                                "d2h_one_gpu_gbs": timed([0], True), "d2h_all_gpus_gbs": timed(every, True),
                                "what": f"256 MiB per GPU, pinned host memory, {world} GPUs at once vs GPU 0 alone"}
                 del bufs
-                vA[:blk // (2 * K) + 1].copy_(sg.A[:blk // (2 * K) + 1]) if sg.nrows else None
             for m in (mA, mB, mD):
                 m.release()
             if not e2e["parity"]["ok"]:

@@ -5,6 +5,8 @@ Reference semantics: the Vector overloads of ``de::blas::cuda::GEMM`` (srcs/modu
 ``de::cuda::Transpose`` (srcs/modules/BLAS/Basic_process/transpose/transpose.cu:50-101) and ``de::cuda::TypeCast``
 (srcs/modules/BLAS/Basic_process/type_cast/GPU_Matrix_type_cast.cu:38-85).
 """
+import ctypes
+
 import torch
 
 from . import capi
@@ -72,4 +74,33 @@ def cast(src, dtype, out=None):
     with torch.cuda.device(src.device):
         capi.check(capi.lib.decxb200_cast2d(kind, torch.cuda.current_stream().cuda_stream, rows, cols, src.data_ptr(),
                                             _ld(src), out.data_ptr(), _ld(out)))
+    return out
+
+
+def conv2d(src, kernels, strides=(1, 1), extend=0, out=None, workspace=None, status=None):
+    """fp32 cross-correlation ``out[y, x, t] = sum src[y*sy+i-py, x*sx+j-px, c] * kernels[t, i, j, c]`` of an
+    H x W x C tensor with n kernels of kh x kw x C (``de::nn::cuda::Conv2D``); ``extend`` 0 = no border,
+    2 = zero border.  Tensors are channels-innermost and may be pitched views.  Launches on the current stream."""
+    if not src.is_cuda or src.dtype != torch.float32 or kernels.dtype != torch.float32:
+        raise TypeError("conv2d takes float32 CUDA tensors")
+    H, W, C = src.shape
+    n, kh, kw, C2 = kernels.shape
+    if C2 != C or src.stride(2) != 1 or kernels.stride(3) != 1:
+        raise ValueError("src is H x W x C, kernels n x kh x kw x C, channels innermost")
+    sx, sy = strides
+    oh, ow = ctypes.c_uint32(), ctypes.c_uint32()
+    capi.check(capi.lib.decxb200_conv2d_fp32_out_dims(H, W, kh, kw, sx, sy, extend, ctypes.byref(oh), ctypes.byref(ow)))
+    if out is None:
+        out = torch.empty((oh.value, ow.value, n), dtype=torch.float32, device=src.device)
+    src_dp, src_wp = src.stride(1), src.stride(0) // src.stride(1)
+    k_dp, k_wp = kernels.stride(2), kernels.stride(1) // kernels.stride(2)
+    dst_dp, dst_wp = out.stride(1), out.stride(0) // out.stride(1)
+    need = int(capi.lib.decxb200_conv2d_fp32_workspace_bytes(H, W, C, kh, kw, n, sx, sy, extend, dst_wp))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        capi.check(capi.lib.decxb200_conv2d_fp32(
+            torch.cuda.current_stream().cuda_stream, src.data_ptr(), H, W, C, src_wp, src_dp, kernels.data_ptr(), kh, kw, n,
+            k_wp, k_dp, kernels.stride(0), out.data_ptr(), dst_wp, dst_dp, sx, sy, extend, workspace.data_ptr(), need,
+            status.data_ptr() if status is not None else None))
     return out

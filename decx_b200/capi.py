@@ -79,6 +79,13 @@ def _load():
     lib.decxb200_transpose.argtypes = [ci, vp, u32, u32, vp, u64, vp, u64]
     lib.decxb200_cast2d.restype = ci
     lib.decxb200_cast2d.argtypes = [ci, vp, u32, u32, vp, u64, vp, u64]
+    lib.decxb200_conv2d_fp32_out_dims.restype = ci
+    lib.decxb200_conv2d_fp32_out_dims.argtypes = [u32, u32, u32, u32, u32, u32, ci, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+    lib.decxb200_conv2d_fp32_workspace_bytes.restype = sz
+    lib.decxb200_conv2d_fp32_workspace_bytes.argtypes = [u32, u32, u32, u32, u32, u32, u32, u32, ci, u32]
+    lib.decxb200_conv2d_fp32.restype = ci
+    lib.decxb200_conv2d_fp32.argtypes = [vp, vp, u32, u32, u32, u32, u32, vp, u32, u32, u32, u32, u32, u64, vp, u32, u32,
+                                         u32, u32, ci, vp, sz, vp]
     lib.decxb200_copy2d_async.restype = ci
     lib.decxb200_copy2d_async.argtypes = [vp, vp, sz, vp, sz, sz, sz]
     lib.decxb200_write_flag_async.restype = ci
@@ -116,7 +123,7 @@ EXPORTS = [
     "decxb200_gemm_host_arena_bytes", "decxb200_gemm_host", "decxb200_gemm_host_multi_arena_bytes", "decxb200_gemm_host_multi_plan",
     "decxb200_gemm_host_multi",
     "decxb200_gemm_fp32_noalloc", "decxb200_gemv_workspace_bytes", "decxb200_gemv", "decxb200_transpose",
-    "decxb200_cast2d",
+    "decxb200_cast2d", "decxb200_conv2d_fp32_out_dims", "decxb200_conv2d_fp32_workspace_bytes", "decxb200_conv2d_fp32",
     "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_tensor_map_cache_stats", "decxb200_debug_stats", "decxb200_strerror", "decxb200_version",

@@ -6,6 +6,7 @@
 #include "../../include/decx_b200.h"
 #include "capi_shared.h"
 #include "gemm_f64.cuh"
+#include "conv2d.cuh"
 #include "gemv.cuh"
 #include "transpose_cast.cuh"
 
@@ -191,6 +192,91 @@ int decxb200_cast2d(int kind, void* stream_, uint32_t rows, uint32_t cols, const
 #undef DXB_CAST
     dxb_host::count_launch();
     return last_error();
+}
+
+// ------------------------------------------------------------------------------------------------ conv2d
+static int conv2d_geometry(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint32_t kw, uint32_t sx, uint32_t sy, int extend,
+                           uint32_t dst_wpitch, Conv2dGeom& g) {
+    if (H == 0 || W == 0 || C == 0 || kh == 0 || kw == 0 || sx == 0 || sy == 0) return DECXB200_EINVAL;
+    memset(&g, 0, sizeof(g));
+    g.H = H; g.W = W; g.C = C; g.kh = kh; g.kw = kw; g.sx = sx; g.sy = sy;
+    if (extend == DECXB200_EXTEND_NONE) {
+        if (kh > H || kw > W) return DECXB200_EINVAL;
+        g.OH = (H - kh + 1) / sy;
+        g.OW = (W - kw + 1) / sx;
+        g.Hlim = H;
+    } else if (extend == DECXB200_EXTEND_CONSTANT) {
+        g.OH = H / sy;
+        g.OW = W / sx;
+        g.py = kh / 2;
+        g.px = kw / 2;
+        g.Hlim = g.OH * sy;
+    } else {
+        return DECXB200_EINVAL;
+    }
+    if (g.OH == 0 || g.OW == 0) return DECXB200_EINVAL;
+    g.dst_wpitch = dst_wpitch ? dst_wpitch : g.OW;
+    if (g.dst_wpitch < g.OW) return DECXB200_EINVAL;
+    const uint64_t kc = uint64_t(kh) * kw * C, rows = uint64_t(g.OH) * g.dst_wpitch;
+    if (kc > 0xFFFFFFFFull || rows > 0xFFFFFFFFull) return DECXB200_ETOOLARGE;
+    g.Kc = uint32_t(kc);
+    return 0;
+}
+
+int decxb200_conv2d_fp32_out_dims(uint32_t H, uint32_t W, uint32_t kh, uint32_t kw, uint32_t sx, uint32_t sy, int extend,
+                                  uint32_t* OH, uint32_t* OW) {
+    Conv2dGeom g;
+    const int rc = conv2d_geometry(H, W, 1, kh, kw, sx, sy, extend, 0, g);
+    if (rc != 0) return rc;
+    if (OH) *OH = g.OH;
+    if (OW) *OW = g.OW;
+    return 0;
+}
+
+size_t decxb200_conv2d_fp32_workspace_bytes(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint32_t kw, uint32_t n_kernels,
+                                            uint32_t sx, uint32_t sy, int extend, uint32_t dst_wpitch) {
+    Conv2dGeom g;
+    if (n_kernels == 0 || conv2d_geometry(H, W, C, kh, kw, sx, sy, extend, dst_wpitch, g) != 0) return 0;
+    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch;
+    const uint64_t a = round_up(M * round_up(g.Kc, 32) * 4, 256), b = round_up(uint64_t(g.Kc) * round_up(n_kernels, 32) * 4, 256);
+    return size_t(a + b + round_up(decxb200_gemm_workspace_bytes(DECXB200_FP32, uint32_t(M), n_kernels, g.Kc), 256));
+}
+
+int decxb200_conv2d_fp32(void* stream_, const void* src, uint32_t H, uint32_t W, uint32_t C, uint32_t src_wpitch,
+                         uint32_t src_dpitch, const void* kernels, uint32_t kh, uint32_t kw, uint32_t n_kernels,
+                         uint32_t kernel_wpitch, uint32_t kernel_dpitch, uint64_t kernel_stride, void* dst,
+                         uint32_t dst_wpitch, uint32_t dst_dpitch, uint32_t sx, uint32_t sy, int extend, void* workspace,
+                         size_t workspace_bytes, unsigned* status) {
+    dxb_host::reset_launches();
+    Conv2dGeom g;
+    if (src == nullptr || kernels == nullptr || dst == nullptr || n_kernels == 0) return DECXB200_EINVAL;
+    int rc = conv2d_geometry(H, W, C, kh, kw, sx, sy, extend, dst_wpitch, g);
+    if (rc != 0) return rc;
+    if (src_wpitch < W || src_dpitch < C || kernel_wpitch < kw || kernel_dpitch < C || dst_dpitch < n_kernels)
+        return DECXB200_EINVAL;
+    g.src_wpitch = src_wpitch;
+    g.src_dpitch = src_dpitch;
+    const size_t need = decxb200_conv2d_fp32_workspace_bytes(H, W, C, kh, kw, n_kernels, sx, sy, extend, dst_wpitch);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return DECXB200_EWORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch, lda = round_up(g.Kc, 32), ldb = round_up(n_kernels, 32);
+    uint8_t* w = static_cast<uint8_t*>(workspace);
+    float* A = reinterpret_cast<float*>(w);
+    float* B = reinterpret_cast<float*>(w + round_up(M * lda * 4, 256));
+    uint8_t* gw = w + round_up(M * lda * 4, 256) + round_up(uint64_t(g.Kc) * ldb * 4, 256);
+    const int vec = aligned16(src) && (src_dpitch % 4) == 0 && (C % 4) == 0;
+    auto blocks = [](uint64_t work) { return unsigned(work / 256 + 1 > 148ull * 32 ? 148ull * 32 : work / 256 + 1); };
+    im2col_fp32_kernel<<<blocks(M * g.kh * g.kw * ((C + 3) / 4)), 256, 0, s>>>(static_cast<const float*>(src), A, lda, g, vec);
+    pack_kernels_kernel<<<blocks(uint64_t(g.Kc) * n_kernels), 256, 0, s>>>(static_cast<const float*>(kernels), kernel_stride,
+                                                                             kernel_wpitch, kernel_dpitch, kh, kw, C, n_kernels,
+                                                                             B, ldb);
+    if ((rc = last_error()) != 0) return rc;
+    const size_t gbytes = decxb200_gemm_workspace_bytes(DECXB200_FP32, uint32_t(M), n_kernels, g.Kc);
+    rc = decxb200_gemm(DECXB200_FP32, stream_, uint32_t(M), n_kernels, g.Kc, A, lda, B, ldb, nullptr, 0, dst, dst_dpitch, nullptr,
+                       nullptr, gw, gbytes, status);
+    dxb_host::count_launch(2);
+    return rc;
 }
 
 }  // extern "C"

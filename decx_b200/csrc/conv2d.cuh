@@ -1,0 +1,79 @@
+// fp32 2-D convolution as im2col + GEMM (reference: de::nn::cuda::Conv2D, srcs/modules/NN/convolution/CUDA/fp32/
+// Conv2D.cu:57-131; planner cuda_conv2D_fp32_im2col_planner.cu:200-300; kernels im2col_fp32.cu, im2col_GEMM_fp32.cu).
+//
+// Tensors are stored channels-innermost: element (y, x, c) at base[(y * wpitch + x) * dpitch + c], the layout of
+// decx::_tensor_layout (srcs/common/Classes/Tensor.h:59-82).  Like the reference the operation is a cross-correlation
+// (no kernel flip):   dst(y, x, t) = sum_{i, j, c} src(y * sy + i - py, x * sx + j - px, c) * kernel_t(i, j, c)
+// with (py, px) = (0, 0) and OH = (H - kh + 1) / sy, OW = (W - kw + 1) / sx for extend = none, and
+// (py, px) = (kh / 2, kw / 2), zeros outside the source, OH = H / sy, OW = W / sx for extend = constant.  In that mode
+// the reference's im2col also reads source rows at and below OH * sy as zeros (the bound of cu_im2col_*_BC_fp32,
+// im2col_fp32.cu:132, is conv2D_area.y * strides.y + kh / 2 in extended coordinates); `Hlim` keeps that.
+//
+// Two bandwidth-bound passes build the operands of ONE dense contraction on the tensor-core path (3xTF32):
+//   im2col_fp32_kernel   A[m][(i * kw + j) * C + c], m = y * dst_wpitch + x (rows of dst's pitch padding are zero)
+//   pack_kernels_kernel  B[(i * kw + j) * C + c][t]
+// and the GEMM writes D = A . B straight into dst (row pitch dst_dpitch).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace dxb {
+
+struct Conv2dGeom {
+    uint32_t H, W, C, src_wpitch, src_dpitch;
+    uint32_t kh, kw, sx, sy, py, px;
+    uint32_t OH, OW, dst_wpitch;
+    uint32_t Kc;             // kh * kw * C
+    uint32_t Hlim;           // source rows >= Hlim read as zero
+};
+
+// one thread per (output position m, tap, group of 4 channels)
+__global__ void im2col_fp32_kernel(const float* __restrict__ src, float* __restrict__ A, uint64_t lda, Conv2dGeom g, int vec_ok) {
+    const uint32_t groups_c = (g.C + 3) / 4;
+    const uint32_t per_row = g.kh * g.kw * groups_c;
+    const uint64_t rows = uint64_t(g.OH) * g.dst_wpitch;
+    const uint64_t total = rows * per_row;
+    for (uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; idx < total; idx += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t m = idx / per_row;
+        const uint32_t r = uint32_t(idx % per_row);
+        const uint32_t tap = r / groups_c, c = (r % groups_c) * 4;
+        const uint32_t i = tap / g.kw, j = tap % g.kw;
+        const uint32_t y = uint32_t(m / g.dst_wpitch), x = uint32_t(m % g.dst_wpitch);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int64_t sy_ = int64_t(y) * g.sy + i - g.py, sx_ = int64_t(x) * g.sx + j - g.px;
+        if (x < g.OW && sy_ >= 0 && sy_ < int64_t(g.Hlim) && sx_ >= 0 && sx_ < int64_t(g.W)) {
+            const float* p = src + (uint64_t(sy_) * g.src_wpitch + uint64_t(sx_)) * g.src_dpitch + c;
+            if (vec_ok && c + 4 <= g.C) v = __ldg(reinterpret_cast<const float4*>(p));
+            else {
+                v.x = p[0];
+                if (c + 1 < g.C) v.y = p[1];
+                if (c + 2 < g.C) v.z = p[2];
+                if (c + 3 < g.C) v.w = p[3];
+            }
+        }
+        float* q = A + m * lda + uint64_t(tap) * g.C + c;
+        if (vec_ok && c + 4 <= g.C) *reinterpret_cast<float4*>(q) = v;
+        else {
+            q[0] = v.x;
+            if (c + 1 < g.C) q[1] = v.y;
+            if (c + 2 < g.C) q[2] = v.z;
+            if (c + 3 < g.C) q[3] = v.w;
+        }
+    }
+}
+
+// kernels: n tensors kh x kw x C (kernel_wpitch, kernel_dpitch), tensor t at kernels + t * kernel_stride (floats)
+__global__ void pack_kernels_kernel(const float* __restrict__ kernels, uint64_t kernel_stride, uint32_t kernel_wpitch,
+                                    uint32_t kernel_dpitch, uint32_t kh, uint32_t kw, uint32_t C, uint32_t n,
+                                    float* __restrict__ B, uint64_t ldb) {
+    const uint64_t Kc = uint64_t(kh) * kw * C, total = Kc * n;
+    for (uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; idx < total; idx += uint64_t(gridDim.x) * blockDim.x) {
+        const uint32_t t = uint32_t(idx % n);
+        const uint64_t k = idx / n;
+        const uint32_t c = uint32_t(k % C), tap = uint32_t(k / C);
+        const uint32_t i = tap / kw, j = tap % kw;
+        B[k * ldb + t] = kernels[t * kernel_stride + (uint64_t(i) * kernel_wpitch + j) * kernel_dpitch + c];
+    }
+}
+
+}  // namespace dxb

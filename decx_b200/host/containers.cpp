@@ -15,9 +15,10 @@
 namespace {
 // Host matrices of 64 MiB and more get their pages interleaved over the NUMA nodes of the machine (mbind,
 // MPOL_INTERLEAVE, before the first touch).  A matrix that one thread allocates and zero-fills would otherwise live
-// on that thread's node alone, and every GPU behind the other socket would pull its rows across the inter-socket
-// link: with eight GPUs moving their row blocks at once that link, not PCIe, set the pace of the host-matrix GEMM.
-// Best effort: any failure leaves the default placement.
+// on that thread's node alone, so every GPU behind the other socket would pull its rows across the inter-socket
+// link when all GPUs move their row blocks at once.  A precaution: on the eight-GPU machine this was measured on,
+// the aggregate host-to-device rate was the same with and without it.  Best effort: any failure leaves the default
+// placement.
 void interleave_pages(void* addr, uint64_t bytes) {
 #if defined(__linux__) && defined(SYS_mbind)
     unsigned long mask = 0;

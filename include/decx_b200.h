@@ -227,6 +227,39 @@ DECXB200_API int decxb200_cast2d(int kind, void* stream, uint32_t rows, uint32_t
                                  const void* src, uint64_t lds, void* dst, uint64_t ldd);
 
 /*
+ * fp32 2-D convolution as im2col + one 3xTF32 GEMM: the consumer of the GEMM core in DECX's NN module
+ * (reference: de::nn::cuda::Conv2D, srcs/modules/NN/convolution/CUDA/fp32/Conv2D.cu:57-131, planner
+ * cuda_conv2D_fp32_im2col_planner.cu:200-300, kernels im2col_fp32.cu and im2col_GEMM_fp32.cu).  Tensors are stored
+ * channels-innermost, element (y, x, c) at base[(y * wpitch + x) * dpitch + c] (srcs/common/Classes/Tensor.h:59-82).
+ * Like the reference it is a cross-correlation (no kernel flip):
+ *     dst(y, x, t) = sum_{i, j, c} src(y*sy + i - py, x*sx + j - px, c) * kernel_t(i, j, c)
+ *   extend = DECXB200_EXTEND_NONE:      py = px = 0,  OH = (H - kh + 1) / sy,  OW = (W - kw + 1) / sx
+ *   extend = DECXB200_EXTEND_CONSTANT:  py = kh / 2, px = kw / 2, zeros outside src,  OH = H / sy,  OW = W / sx;
+ *                                       source rows at and below OH * sy also read as zeros, as in the reference
+ *                                       (im2col_fp32.cu:132)
+ * (the values of de::extend_label, srcs/includes/DECX/basic_proc/VectorProc.h:22-26).  kernels: n_kernels tensors of
+ * kh x kw x C, tensor t at kernels + t * kernel_stride floats.  dst: OH x OW x n_kernels with dst_wpitch (0 = OW) and
+ * dst_dpitch >= n_kernels; positions x in [OW, dst_wpitch) of every dst row are written with zeros.  All device
+ * pointers; asynchronous on `stream`; workspace (256-byte aligned) holds the im2col matrix, the packed kernels and the
+ * GEMM's tf32 planes.  The tensor containers (de::GPU_Tensor, de::GPU_TensorArray) are not part of this library: this
+ * entry point is what the reference's conv2D_im2col_fp32_caller would bind.
+ */
+#define DECXB200_EXTEND_NONE 0
+#define DECXB200_EXTEND_CONSTANT 2
+DECXB200_API int decxb200_conv2d_fp32_out_dims(uint32_t H, uint32_t W, uint32_t kh, uint32_t kw, uint32_t sx, uint32_t sy,
+                                               int extend, uint32_t* OH, uint32_t* OW);
+DECXB200_API size_t decxb200_conv2d_fp32_workspace_bytes(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint32_t kw,
+                                                         uint32_t n_kernels, uint32_t sx, uint32_t sy, int extend,
+                                                         uint32_t dst_wpitch);
+DECXB200_API int decxb200_conv2d_fp32(void* stream, const void* src, uint32_t H, uint32_t W, uint32_t C,
+                                      uint32_t src_wpitch, uint32_t src_dpitch,
+                                      const void* kernels, uint32_t kh, uint32_t kw, uint32_t n_kernels,
+                                      uint32_t kernel_wpitch, uint32_t kernel_dpitch, uint64_t kernel_stride,
+                                      void* dst, uint32_t dst_wpitch, uint32_t dst_dpitch,
+                                      uint32_t sx, uint32_t sy, int extend,
+                                      void* workspace, size_t workspace_bytes, unsigned* status);
+
+/*
  * Peer-visible device buffers for the row-sharded multi-GPU GEMM (one process per GPU).
  * The owner of the result allocates D with decxb200_ipc_alloc and exports a 64-byte handle;
  * every other rank opens it and passes `peer_ptr + its row offset` as the D argument of

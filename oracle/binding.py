@@ -55,6 +55,8 @@ def lib():
         ci = ctypes.c_int
         L.oracle_gemv_f32.argtypes = [ci, u32, u32, vp, sz, vp, vp]
         L.oracle_gemv_f16.argtypes = [ci, u32, u32, vp, sz, vp, vp, vp, vp]
+        L.oracle_conv2d_f32.argtypes = [u32, u32, u32, vp, u32, u32, u32, vp, u32, u32, ci, u32, u32, vp, vp]
+        L.oracle_conv2d_f32.restype = ci
         L.oracle_gemm_f64.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, d, d, vp, sz]
         L.oracle_gemm_c64.argtypes = [u32, u32, u32, vp, sz, vp, sz, vp, sz, vp, vp, vp, sz]
         _lib = L
@@ -128,6 +130,29 @@ def gemv(A, x, trans=False):
         L.oracle_gemv_f16(int(trans), rows, cols, _p(A), cols, _p(x), _p(y32), _p(y64), _p(mag))
         return y32, y64, mag
     raise TypeError(A.dtype)
+
+
+def conv2d_dims(H, W, kh, kw, strides=(1, 1), extend=0):
+    """Output (OH, OW) of the reference's Conv2D (cuda_conv2D_fp32_im2col_planner.cu:215-225)."""
+    sx, sy = strides
+    if extend == 0:
+        return (H - kh + 1) // sy, (W - kw + 1) // sx
+    return H // sy, W // sx
+
+
+def conv2d(src, kernels, strides=(1, 1), extend=0):
+    """Oracle cross-correlation of src (H, W, C) with kernels (n, kh, kw, C): (fp64 result (OH, OW, n), sum of
+    |products| per output).  extend 0 = no border, 2 = zero border of (kh // 2, kw // 2)."""
+    L = lib()
+    src, kernels = _c(src, np.float32), _c(kernels, np.float32)
+    H, W, C = src.shape
+    n, kh, kw, _ = kernels.shape
+    OH, OW = conv2d_dims(H, W, kh, kw, strides, extend)
+    D, mag = np.empty((OH, OW, n), np.float64), np.empty((OH, OW, n), np.float64)
+    rc = L.oracle_conv2d_f32(H, W, C, _p(src), kh, kw, n, _p(kernels), strides[0], strides[1], extend, OH, OW, _p(D), _p(mag))
+    if rc != 0:
+        raise ValueError("oracle_conv2d_f32: %d" % rc)
+    return D, mag
 
 
 def to_half(x):

@@ -1,5 +1,6 @@
 /*
- * TEST INFRASTRUCTURE ONLY -- CPU restatement of the matrix-vector products and of the fp64 GEMMs.
+ * TEST INFRASTRUCTURE ONLY -- CPU restatement of the matrix-vector products, of the fp64 GEMMs and of the fp32
+ * 2-D convolution (parity unpinned for the convolution, see its function).
  * Only tests, the smoke check and the benchmark's cpu_baseline leg may call this file.
  *
  * What it restates (reference, file:line within param0037/DECX):
@@ -113,4 +114,53 @@ ORACLE_API void oracle_gemm_c64(uint32_t M, uint32_t N, uint32_t K, const double
             D[2 * (i * ldd + j)] = (double)ore;
             D[2 * (i * ldd + j) + 1] = (double)oim;
         }
+}
+
+/* Direct 2-D cross-correlation, fp64 accumulation (reference: de::nn::cuda::Conv2D, srcs/modules/NN/convolution/CUDA/
+ * fp32/Conv2D.cu:57-131; output dims cuda_conv2D_fp32_im2col_planner.cu:215-225; zero border of kh/2, kw/2 and the
+ * bottom bound OH*sy of im2col_fp32.cu:122-132).  Dense tensors: src H x W x C, kernels n x kh x kw x C,
+ * dst OH x OW x n; mag = sum |src||kernel| per output (error scale).  extend: 0 none, 2 constant.
+ * PARITY UNPINNED: the reference has no CPU Conv2D, test or golden vector; this follows a reading of its CUDA path and
+ * is cross-checked against an independent numpy formulation only. */
+ORACLE_API int oracle_conv2d_f32(uint32_t H, uint32_t W, uint32_t C, const float* src, uint32_t kh, uint32_t kw, uint32_t n,
+                                 const float* ker, uint32_t sx, uint32_t sy, int extend, uint32_t OH, uint32_t OW, double* dst,
+                                 double* mag) {
+    uint32_t eh, ew, py = 0, px = 0, hlim = H;
+    if (extend == 0) {
+        if (kh > H || kw > W) return -1;
+        eh = (H - kh + 1) / sy;
+        ew = (W - kw + 1) / sx;
+    } else if (extend == 2) {
+        eh = H / sy;
+        ew = W / sx;
+        py = kh / 2;
+        px = kw / 2;
+        hlim = eh * sy;
+    } else {
+        return -1;
+    }
+    if (eh != OH || ew != OW) return -2;
+    for (uint32_t y = 0; y < OH; ++y)
+        for (uint32_t x = 0; x < OW; ++x)
+            for (uint32_t t = 0; t < n; ++t) {
+                double s = 0.0, m = 0.0;
+                for (uint32_t i = 0; i < kh; ++i) {
+                    const int64_t yy = (int64_t)y * sy + i - py;
+                    if (yy < 0 || yy >= (int64_t)hlim) continue;
+                    for (uint32_t j = 0; j < kw; ++j) {
+                        const int64_t xx = (int64_t)x * sx + j - px;
+                        if (xx < 0 || xx >= (int64_t)W) continue;
+                        const float* a = src + ((size_t)yy * W + (size_t)xx) * C;
+                        const float* b = ker + (((size_t)t * kh + i) * kw + j) * C;
+                        for (uint32_t c = 0; c < C; ++c) {
+                            const double p = (double)a[c] * (double)b[c];
+                            s += p;
+                            m += p < 0 ? -p : p;
+                        }
+                    }
+                }
+                dst[((size_t)y * OW + x) * n + t] = s;
+                mag[((size_t)y * OW + x) * n + t] = m;
+            }
+    return 0;
 }
