@@ -63,6 +63,8 @@ def test_host_units_under_sanitizers(tmp_path, san):
     stub = tmp_path / "abi_stub.cpp"       # the unit tests call the GEMM entry only to see its "not initialised" error
     stub.write_text('#include "DECX.h"\n#include "decx_b200/host/internal.h"\n'
                     'void de::blas::cuda::GEMM(de::Matrix&, de::Matrix&, de::Matrix&) {\n'
+                    '    decx::err::set(de::GetLastError(), de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first"); }\n'
+                    'void de::blas::cuda::GEMM(de::Matrix&, de::Matrix&, de::Matrix&, de::Matrix&) {\n'
                     '    decx::err::set(de::GetLastError(), de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first"); }\n')
     exe = str(tmp_path / "host_units_san")
     cmd = ["g++", "-std=c++17", "-O1", "-g", f"-fsanitize={san}", "-fno-omit-frame-pointer", "-I", os.path.join(ROOT, "include"),
