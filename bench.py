@@ -58,6 +58,8 @@ AUX = {
     "cast_f16_f32": ("cast", "float16", 16384, 16384, {"to": "float32"}),
     "gemm_f64_4096": ("gemm64", "float64", 4096, 4096, {"K": 4096, "ff": 2}),
     "gemm_c128_2048": ("gemm64", "complex128", 2048, 2048, {"K": 2048, "ff": 8}),
+    # rows x cols = H x W of the source tensor; zero border, stride 1
+    "conv2d_f32_512x512x64_k3_n128": ("conv", "float32", 512, 512, {"C": 64, "n": 128, "k": 3}),
 }
 FP64_NOMINAL_TFLOPS = 40.0      # B200 datasheet fp64 (vector and tensor); no measured fp64 peak exists for this pool
 
@@ -237,10 +239,11 @@ def variant_name(v):
     """decxb200_last_kernel_variant() -> the kernel's template name."""
     if not v:
         return None
+    narrow, v = divmod(v, 5000)
     fetch, v = divmod(v, 1000)
     kind, rest = divmod(v, 100)
     ctas, nacc = divmod(rest, 10)
-    return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}>"
+    return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}{',64' if narrow else ''}>"
 
 
 def hbm_peak():
@@ -281,6 +284,14 @@ def time_aux(torch, name, device, iters=10, warmup=3):
         out = torch.empty((rows, cols), dtype=to, device=device)
         run = lambda: Bl.cast(A, to, out=out)
         work, unit, bound = rows * cols * (esz + out.element_size()), "GB/s", "hbm"
+    elif kind == "conv":
+        C, n, k = ex["C"], ex["n"], ex["k"]
+        src, ker = rnd((rows, cols, C), tdt), rnd((n, k, k, C), tdt)
+        out = Bl.conv2d(src, ker, (1, 1), 2)
+        need = int(capi_lib().decxb200_conv2d_fp32_workspace_bytes(rows, cols, C, k, k, n, 1, 1, 2, 0))
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        run = lambda: Bl.conv2d(src, ker, (1, 1), 2, out=out, workspace=ws)
+        work, unit, bound = 2 * rows * cols * k * k * C * n, "TFLOP/s", "tensor (3xTF32) behind an HBM-bound im2col pass"
     else:
         K = ex["K"]
         A, B = rnd((rows, K), tdt), rnd((K, cols), tdt)
@@ -304,6 +315,9 @@ def time_aux(torch, name, device, iters=10, warmup=3):
     if unit == "GB/s":
         achieved = work / (med * 1e-3) / 1e9
         peak, src = hbm_peak()
+    elif kind == "conv":
+        achieved = work / (med * 1e-3) / 1e12
+        peak, src = peaks()["bf16"] / 6.0, "measured bf16 burst / 6 (3xTF32); whole call, im2col pass included"
     else:
         achieved = work / (med * 1e-3) / 1e12
         peak, src = FP64_NOMINAL_TFLOPS, "nominal B200 fp64 (no measured fp64 peak for this pool)"

@@ -46,7 +46,7 @@ constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
     unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
-    bool attr_set[2][2][2][2] = {};
+    bool attr_set[2][2][2][4] = {};
 };
 DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
@@ -131,9 +131,9 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
     return r == CUDA_SUCCESS ? 0 : DECXB200_EDRIVER;
 }
 
-template <int KIND, int CTAS, int NACC = 1, int FETCH = 0>
+template <int KIND, int CTAS, int NACC = 1, int FETCH = 0, int BNV = 256>
 int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                const CUtensorMap& b1, GemmParams p, int max_ctas, const FetchParams* fetch = nullptr) {
+                const CUtensorMap& b1, GemmParams p, int max_ctas, const FetchParams* fetch = nullptr, bool pdl = false) {
     // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
     // that is what makes the stores efficient when D lives in another GPU's memory; DECXB200_TMA_STORE=0 disables
     static const int tma_store_env = [] { const char* e = getenv("DECXB200_TMA_STORE"); return e ? atoi(e) : 1; }();
@@ -149,8 +149,8 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
             make_map(&cmap, f16, p.C, p.M, p.N, p.ldc, f16 ? 64 : 32, 32) == 0)
             p.c_tma = 1;
     }
-    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
-    auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC, FETCH>;
+    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH, BNV>;
+    auto kern = gemm_tcgen05_kernel<KIND, CTAS, NACC, FETCH, BNV>;
     FetchParams f;
     memset(&f, 0, sizeof(f));
     if (fetch != nullptr) f = *fetch;
@@ -161,10 +161,10 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
             cudaError_t e = cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess) return int(e);
         }
-        if (!di.attr_set[KIND][CTAS - 1][NACC - 1][FETCH ? 1 : 0]) {
+        if (!di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV != 256 ? 2 : 0)]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
             if (e != cudaSuccess) return int(e);
-            di.attr_set[KIND][CTAS - 1][NACC - 1][FETCH ? 1 : 0] = true;
+            di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV != 256 ? 2 : 0)] = true;
         }
     }
     p.tiles_m = uint32_t((uint64_t(p.M) + Cfg::BM * CTAS - 1) / (Cfg::BM * CTAS));
@@ -212,17 +212,25 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // The kernel just before this one in the stream is the pass that writes the operand planes: let this kernel's
+    // CTAs start (barriers, tensor memory) while that pass drains; they wait for it before their first load.
+    static const int pdl_env = [] { const char* e = getenv("DECXB200_PDL"); return e ? atoi(e) : 1; }();
+    if (pdl && pdl_env != 0 && KIND == 1) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, cmap, p, f);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
-    t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0);
+    t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0) + (BNV != 256 ? 5000 : 0);
     return 0;
 }
 
@@ -293,6 +301,18 @@ int prep_a(cudaStream_t stream, bool cplx, const void* A, uint64_t lda, uint32_t
     const int vec = ((ldx % 4) == 0 && aligned16(A)) ? 1 : 0;
     split_tf32_kernel<<<prepass_blocks(uint64_t(M) * ((Kr + 3) / 4)), 256, 0, stream>>>(
         static_cast<const float*>(A), ldx, M, Kr, a_hi, a_lo, ldaw, vec);
+    ++t_launches;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+// tf32 planes of both operands of a real product in one launch
+int prep_ab(cudaStream_t stream, const void* A, uint64_t lda, const void* B, uint64_t ldb, uint32_t M, uint32_t N, uint32_t K,
+            float* a_hi, float* a_lo, uint64_t ldaw, float* b_hi, float* b_lo, uint64_t ldbw) {
+    const SplitJob ja{static_cast<const float*>(A), lda, M, K, a_hi, a_lo, ldaw, ((lda % 4) == 0 && aligned16(A)) ? 1 : 0};
+    const SplitJob jb{static_cast<const float*>(B), ldb, K, N, b_hi, b_lo, ldbw, ((ldb % 4) == 0 && aligned16(B)) ? 1 : 0};
+    const uint64_t work = uint64_t(M) * ((K + 3) / 4) + uint64_t(K) * ((N + 3) / 4);
+    split_tf32_pair_kernel<<<prepass_blocks(work), 256, 0, stream>>>(ja, jb);
     ++t_launches;
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : int(e);
@@ -428,7 +448,8 @@ int run_f16(cudaStream_t stream, int dev, uint32_t M, uint32_t N, uint32_t K, co
 // M x Nr x Kr real 3xTF32 product of pre-split planes (complex: Nr = 2N, Kr = 2K; ldc/ldd in elements)
 int run_tf32(cudaStream_t stream, int dev, bool cplx, uint32_t M, uint32_t N, uint32_t K, const float* a_hi,
              const float* a_lo, uint64_t ldaw, const float* b_hi, const float* b_lo, uint64_t ldbw, const void* C,
-             uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc, unsigned* status, int cta_group, int max_ctas) {
+             uint64_t ldc, void* D, uint64_t ldd, const Scalars& sc, unsigned* status, int cta_group, int max_ctas,
+             bool pdl = false) {
     const uint32_t Kr = cplx ? 2 * K : K, Nr = cplx ? 2 * N : N;
     GemmParams p;
     fill_common(p, sc, C, D, status);
@@ -445,15 +466,23 @@ int run_tf32(cudaStream_t stream, int dev, bool cplx, uint32_t M, uint32_t N, ui
     if ((rc = make_map(&a1, false, a_lo, M, Kr, ldaw, C1::BK, C1::BM)) != 0) return rc;
     // the planes are padded to whole 32-float chunks (ldbw), so the one-load-per-stage form is always legal
     p.b_chunked_map = 1;
-    const uint32_t chunks = (cta_group == 1) ? GemmCfg<1, 1>::B_CHUNKS : GemmCfg<1, 2>::B_CHUNKS;
+    // Small problems: 128 x 256 tiles would leave most SMs without one (fp32 1024^3: 32 tiles on 148 SMs), and the
+    // call then lasts as long as one SM needs for its tile.  128 x 64 tiles give four times as many.
+    static const int narrow_env = [] { const char* e = getenv("DECXB200_NARROW"); return e ? atoi(e) : 1; }();
+    const uint64_t tiles_wide = ((uint64_t(M) + 127) / 128) * ((uint64_t(Nr) + 255) / 256);
+    const bool narrow = narrow_env != 0 && tiles_wide <= 74;
+    if (narrow) cta_group = 1;
+    const uint32_t chunks = narrow ? GemmCfg<1, 1, 1, 0, 64>::B_CHUNKS
+                                   : (cta_group == 1) ? GemmCfg<1, 1>::B_CHUNKS : GemmCfg<1, 2>::B_CHUNKS;
     if ((rc = make_map_b_chunked(&b0, false, b_hi, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, chunks,
                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
     if ((rc = make_map_b_chunked(&b1, false, b_lo, Kr, Nr, ldbw, C1::CHUNK_N, C1::BK, chunks,
                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
-    return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas)
-                          : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas);
+    if (narrow) return launch_gemm<1, 1, 1, 0, 64>(stream, dev, a0, a1, b0, b1, p, max_ctas, nullptr, pdl);
+    return cta_group == 1 ? launch_gemm<1, 1>(stream, dev, a0, a1, b0, b1, p, max_ctas, nullptr, pdl)
+                          : launch_gemm<1, 2>(stream, dev, a0, a1, b0, b1, p, max_ctas, nullptr, pdl);
 }
 
 int check_common(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, const void* B,
@@ -576,6 +605,20 @@ HostArena plan_arena(int dtype, uint32_t M, uint32_t N, uint32_t K, bool has_c) 
 
 }  // namespace
 
+int dxb_host::gemm_tf32_planes(cudaStream_t stream, uint32_t M, uint32_t N, uint32_t K, const float* a_hi,
+                               const float* a_lo, uint64_t ldaw, const float* b_hi, const float* b_lo, uint64_t ldbw,
+                               void* D, uint64_t ldd, unsigned* status) {
+    if (a_hi == nullptr || a_lo == nullptr || b_hi == nullptr || b_lo == nullptr || D == nullptr) return DECXB200_EINVAL;
+    if (M == 0 || N == 0 || K == 0 || ldaw < K || ldbw < N || ldd < N || (ldaw % 32) != 0 || (ldbw % 32) != 0)
+        return DECXB200_EINVAL;
+    int dev = 0;
+    const cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return int(ce);
+    if (dev < 0 || dev >= MAX_DEVICES) return DECXB200_EINVAL;
+    return run_tf32(stream, dev, false, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, nullptr, 0, D, ldd, Scalars(), status,
+                    default_cta_group(), 0);
+}
+
 extern "C" {
 
 int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda,
@@ -612,10 +655,14 @@ int decxb200_gemm_ex(int dtype, void* stream_, uint32_t M, uint32_t N, uint32_t 
     float* a_lo = reinterpret_cast<float*>(w + a_bytes);
     float* b_hi = reinterpret_cast<float*>(w + 2 * a_bytes);
     float* b_lo = reinterpret_cast<float*>(w + 2 * a_bytes + b_bytes);
-    if ((rc = prep_a(stream, cplx, A, lda, M, K, a_hi, a_lo, ldaw)) != 0) return rc;
-    if ((rc = prep_b(stream, cplx, B, ldb, K, N, b_hi, b_lo, ldbw)) != 0) return rc;
+    if (!cplx) {
+        if ((rc = prep_ab(stream, A, lda, B, ldb, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw)) != 0) return rc;
+    } else {
+        if ((rc = prep_a(stream, cplx, A, lda, M, K, a_hi, a_lo, ldaw)) != 0) return rc;
+        if ((rc = prep_b(stream, cplx, B, ldb, K, N, b_hi, b_lo, ldbw)) != 0) return rc;
+    }
     return run_tf32(stream, dev, cplx, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, C, ldc, D, ldd, sc, status,
-                    cta_group, max_ctas);
+                    cta_group, max_ctas, true);
 }
 
 size_t decxb200_gemm_host_arena_bytes(int dtype, uint32_t M, uint32_t N, uint32_t K, int has_c) {

@@ -217,7 +217,8 @@ static int conv2d_geometry(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint
     if (g.OH == 0 || g.OW == 0) return DECXB200_EINVAL;
     g.dst_wpitch = dst_wpitch ? dst_wpitch : g.OW;
     if (g.dst_wpitch < g.OW) return DECXB200_EINVAL;
-    const uint64_t kc = uint64_t(kh) * kw * C, rows = uint64_t(g.OH) * g.dst_wpitch;
+    g.Cp = (C + 3) / 4 * 4;
+    const uint64_t kc = uint64_t(kh) * kw * g.Cp, rows = uint64_t(g.OH) * g.dst_wpitch;
     if (kc > 0xFFFFFFFFull || rows > 0xFFFFFFFFull) return DECXB200_ETOOLARGE;
     g.Kc = uint32_t(kc);
     return 0;
@@ -239,7 +240,7 @@ size_t decxb200_conv2d_fp32_workspace_bytes(uint32_t H, uint32_t W, uint32_t C, 
     if (n_kernels == 0 || conv2d_geometry(H, W, C, kh, kw, sx, sy, extend, dst_wpitch, g) != 0) return 0;
     const uint64_t M = uint64_t(g.OH) * g.dst_wpitch;
     const uint64_t a = round_up(M * round_up(g.Kc, 32) * 4, 256), b = round_up(uint64_t(g.Kc) * round_up(n_kernels, 32) * 4, 256);
-    return size_t(a + b + round_up(decxb200_gemm_workspace_bytes(DECXB200_FP32, uint32_t(M), n_kernels, g.Kc), 256));
+    return size_t(2 * a + 2 * b);
 }
 
 int decxb200_conv2d_fp32(void* stream_, const void* src, uint32_t H, uint32_t W, uint32_t C, uint32_t src_wpitch,
@@ -260,21 +261,22 @@ int decxb200_conv2d_fp32(void* stream_, const void* src, uint32_t H, uint32_t W,
     if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
         return DECXB200_EWORKSPACE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch, lda = round_up(g.Kc, 32), ldb = round_up(n_kernels, 32);
+    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch, ldaw = round_up(g.Kc, 32), ldbw = round_up(n_kernels, 32);
+    const uint64_t a_bytes = round_up(M * ldaw * 4, 256), b_bytes = round_up(uint64_t(g.Kc) * ldbw * 4, 256);
     uint8_t* w = static_cast<uint8_t*>(workspace);
-    float* A = reinterpret_cast<float*>(w);
-    float* B = reinterpret_cast<float*>(w + round_up(M * lda * 4, 256));
-    uint8_t* gw = w + round_up(M * lda * 4, 256) + round_up(uint64_t(g.Kc) * ldb * 4, 256);
-    const int vec = aligned16(src) && (src_dpitch % 4) == 0 && (C % 4) == 0;
+    float* a_hi = reinterpret_cast<float*>(w);
+    float* a_lo = reinterpret_cast<float*>(w + a_bytes);
+    float* b_hi = reinterpret_cast<float*>(w + 2 * a_bytes);
+    float* b_lo = reinterpret_cast<float*>(w + 2 * a_bytes + b_bytes);
+    const int vec = aligned16(src) && (src_dpitch % 4) == 0;
     auto blocks = [](uint64_t work) { return unsigned(work / 256 + 1 > 148ull * 32 ? 148ull * 32 : work / 256 + 1); };
-    im2col_fp32_kernel<<<blocks(M * g.kh * g.kw * ((C + 3) / 4)), 256, 0, s>>>(static_cast<const float*>(src), A, lda, g, vec);
-    pack_kernels_kernel<<<blocks(uint64_t(g.Kc) * n_kernels), 256, 0, s>>>(static_cast<const float*>(kernels), kernel_stride,
-                                                                             kernel_wpitch, kernel_dpitch, kh, kw, C, n_kernels,
-                                                                             B, ldb);
+    im2col_split_kernel<<<blocks(M * g.kh * g.kw * (g.Cp / 4)), 256, 0, s>>>(static_cast<const float*>(src), a_hi, a_lo, ldaw,
+                                                                              g, vec);
+    pack_kernels_split_kernel<<<blocks(uint64_t(g.Kc) * ((n_kernels + 3) / 4)), 256, 0, s>>>(
+        static_cast<const float*>(kernels), kernel_stride, kernel_wpitch, kernel_dpitch, kh, kw, C, g.Cp, n_kernels, b_hi, b_lo,
+        ldbw);
     if ((rc = last_error()) != 0) return rc;
-    const size_t gbytes = decxb200_gemm_workspace_bytes(DECXB200_FP32, uint32_t(M), n_kernels, g.Kc);
-    rc = decxb200_gemm(DECXB200_FP32, stream_, uint32_t(M), n_kernels, g.Kc, A, lda, B, ldb, nullptr, 0, dst, dst_dpitch, nullptr,
-                       nullptr, gw, gbytes, status);
+    rc = dxb_host::gemm_tf32_planes(s, uint32_t(M), n_kernels, g.Kc, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, dst, dst_dpitch, status);
     dxb_host::count_launch(2);
     return rc;
 }

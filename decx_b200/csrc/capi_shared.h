@@ -20,4 +20,10 @@ int run_f64(cudaStream_t stream, bool cplx, uint32_t M, uint32_t N, uint32_t K, 
             const double beta[2], void* workspace, size_t workspace_bytes, bool b_expanded = false);
 size_t f64_workspace_bytes(bool cplx, uint32_t M, uint32_t N, uint32_t K);
 
+// D = A . B in 3xTF32 from operands that a producer kernel already wrote as tf32 (hi, lo) planes: rows ldaw / ldbw
+// floats apart (multiples of 32), planes 256-byte aligned; the planes' padding columns need not be initialised.
+int gemm_tf32_planes(cudaStream_t stream, uint32_t M, uint32_t N, uint32_t K, const float* a_hi, const float* a_lo,
+                     uint64_t ldaw, const float* b_hi, const float* b_lo, uint64_t ldbw, void* D, uint64_t ldd,
+                     unsigned* status);
+
 }  // namespace dxb_host

@@ -9,13 +9,17 @@
 // the reference's im2col also reads source rows at and below OH * sy as zeros (the bound of cu_im2col_*_BC_fp32,
 // im2col_fp32.cu:132, is conv2D_area.y * strides.y + kh / 2 in extended coordinates); `Hlim` keeps that.
 //
-// Two bandwidth-bound passes build the operands of ONE dense contraction on the tensor-core path (3xTF32):
-//   im2col_fp32_kernel   A[m][(i * kw + j) * C + c], m = y * dst_wpitch + x (rows of dst's pitch padding are zero)
-//   pack_kernels_kernel  B[(i * kw + j) * C + c][t]
-// and the GEMM writes D = A . B straight into dst (row pitch dst_dpitch).
+// Two bandwidth-bound passes build the operands of ONE dense contraction on the tensor-core path (3xTF32), already
+// split into the tf32 (hi, lo) planes that contraction reads -- the fp32 im2col matrix itself is never stored:
+//   im2col_split_kernel        A[m][(i * kw + j) * Cp + c], m = y * dst_wpitch + x (rows of dst's pitch padding are zero)
+//   pack_kernels_split_kernel  B[(i * kw + j) * Cp + c][t]
+// with Cp = C rounded up to 4 (zero channels), so that every plane store is a 16-byte store; the GEMM writes
+// D = A . B straight into dst (row pitch dst_dpitch).
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+
+#include "prepass.cuh"
 
 namespace dxb {
 
@@ -23,13 +27,16 @@ struct Conv2dGeom {
     uint32_t H, W, C, src_wpitch, src_dpitch;
     uint32_t kh, kw, sx, sy, py, px;
     uint32_t OH, OW, dst_wpitch;
-    uint32_t Kc;             // kh * kw * C
+    uint32_t Cp;             // C rounded up to a multiple of 4
+    uint32_t Kc;             // kh * kw * Cp
     uint32_t Hlim;           // source rows >= Hlim read as zero
 };
 
-// one thread per (output position m, tap, group of 4 channels)
-__global__ void im2col_fp32_kernel(const float* __restrict__ src, float* __restrict__ A, uint64_t lda, Conv2dGeom g, int vec_ok) {
-    const uint32_t groups_c = (g.C + 3) / 4;
+// one thread per (output position m, tap, group of 4 channels): one 16-byte load, two 16-byte stores
+__global__ void im2col_split_kernel(const float* __restrict__ src, float* __restrict__ a_hi, float* __restrict__ a_lo,
+                                    uint64_t ldaw, Conv2dGeom g, int vec_ok) {
+    allow_dependent_launch();
+    const uint32_t groups_c = g.Cp / 4;
     const uint32_t per_row = g.kh * g.kw * groups_c;
     const uint64_t rows = uint64_t(g.OH) * g.dst_wpitch;
     const uint64_t total = rows * per_row;
@@ -43,36 +50,56 @@ __global__ void im2col_fp32_kernel(const float* __restrict__ src, float* __restr
         const int64_t sy_ = int64_t(y) * g.sy + i - g.py, sx_ = int64_t(x) * g.sx + j - g.px;
         if (x < g.OW && sy_ >= 0 && sy_ < int64_t(g.Hlim) && sx_ >= 0 && sx_ < int64_t(g.W)) {
             const float* p = src + (uint64_t(sy_) * g.src_wpitch + uint64_t(sx_)) * g.src_dpitch + c;
-            if (vec_ok && c + 4 <= g.C) v = __ldg(reinterpret_cast<const float4*>(p));
-            else {
+            if (vec_ok && c + 4 <= g.src_dpitch) {        // the pitch padding may hold anything: masked below
+                v = __ldg(reinterpret_cast<const float4*>(p));
+                if (c + 1 >= g.C) v.y = 0.f;
+                if (c + 2 >= g.C) v.z = 0.f;
+                if (c + 3 >= g.C) v.w = 0.f;
+            } else {
                 v.x = p[0];
                 if (c + 1 < g.C) v.y = p[1];
                 if (c + 2 < g.C) v.z = p[2];
                 if (c + 3 < g.C) v.w = p[3];
             }
         }
-        float* q = A + m * lda + uint64_t(tap) * g.C + c;
-        if (vec_ok && c + 4 <= g.C) *reinterpret_cast<float4*>(q) = v;
-        else {
-            q[0] = v.x;
-            if (c + 1 < g.C) q[1] = v.y;
-            if (c + 2 < g.C) q[2] = v.z;
-            if (c + 3 < g.C) q[3] = v.w;
-        }
+        float4 h, l;
+        split1(v.x, h.x, l.x);
+        split1(v.y, h.y, l.y);
+        split1(v.z, h.z, l.z);
+        split1(v.w, h.w, l.w);
+        const uint64_t o = m * ldaw + uint64_t(tap) * g.Cp + c;
+        *reinterpret_cast<float4*>(a_hi + o) = h;
+        *reinterpret_cast<float4*>(a_lo + o) = l;
     }
 }
 
-// kernels: n tensors kh x kw x C (kernel_wpitch, kernel_dpitch), tensor t at kernels + t * kernel_stride (floats)
-__global__ void pack_kernels_kernel(const float* __restrict__ kernels, uint64_t kernel_stride, uint32_t kernel_wpitch,
-                                    uint32_t kernel_dpitch, uint32_t kh, uint32_t kw, uint32_t C, uint32_t n,
-                                    float* __restrict__ B, uint64_t ldb) {
-    const uint64_t Kc = uint64_t(kh) * kw * C, total = Kc * n;
+// kernels: n tensors kh x kw x C (kernel_wpitch, kernel_dpitch), tensor t at kernels + t * kernel_stride (floats).
+// One thread per (row k of B, group of 4 kernels).
+__global__ void pack_kernels_split_kernel(const float* __restrict__ kernels, uint64_t kernel_stride, uint32_t kernel_wpitch,
+                                          uint32_t kernel_dpitch, uint32_t kh, uint32_t kw, uint32_t C, uint32_t Cp, uint32_t n,
+                                          float* __restrict__ b_hi, float* __restrict__ b_lo, uint64_t ldbw) {
+    allow_dependent_launch();
+    const uint32_t groups = (n + 3) / 4;
+    const uint64_t Kc = uint64_t(kh) * kw * Cp, total = Kc * groups;
     for (uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; idx < total; idx += uint64_t(gridDim.x) * blockDim.x) {
-        const uint32_t t = uint32_t(idx % n);
-        const uint64_t k = idx / n;
-        const uint32_t c = uint32_t(k % C), tap = uint32_t(k / C);
+        const uint32_t t = uint32_t(idx % groups) * 4;
+        const uint64_t k = idx / groups;
+        const uint32_t c = uint32_t(k % Cp), tap = uint32_t(k / Cp);
         const uint32_t i = tap / kw, j = tap % kw;
-        B[k * ldb + t] = kernels[t * kernel_stride + (uint64_t(i) * kernel_wpitch + j) * kernel_dpitch + c];
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (c < C) {
+            const float* p = kernels + (uint64_t(i) * kernel_wpitch + j) * kernel_dpitch + c;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (t + q < n) v[q] = p[uint64_t(t + q) * kernel_stride];
+        }
+        float4 h, l;
+        split1(v[0], h.x, l.x);
+        split1(v[1], h.y, l.y);
+        split1(v[2], h.z, l.z);
+        split1(v[3], h.w, l.w);
+        *reinterpret_cast<float4*>(b_hi + k * ldbw + t) = h;
+        *reinterpret_cast<float4*>(b_lo + k * ldbw + t) = l;
     }
 }
 

@@ -164,14 +164,15 @@ struct FetchParams {
 __device__ unsigned g_wave_ticket;
 
 
-template <int KIND, int CTAS, int NACC = 1, int FETCH = 0>
+template <int KIND, int CTAS, int NACC = 1, int FETCH = 0, int BNV = 256>
 struct GemmCfg {
+    static_assert(BNV == 256 || (BNV == 64 && KIND == 1 && CTAS == 1), "narrow accumulators: 3xTF32 single-CTA tiles only");
     static_assert(NACC == 1 || (NACC == 2 && KIND == 0 && CTAS == 2), "two accumulators per tile: fp16 CTA pairs only");
     static_assert(FETCH == 0 || (KIND == 0 && CTAS == 2), "courier warps: fp16 CTA pairs only");
     static constexpr int ELEM = (KIND == 0) ? 2 : 4;
     static constexpr int NPL = (KIND == 0) ? 1 : 2;       // operand planes (hi, lo)
     static constexpr int BM = 128;                        // rows per CTA
-    static constexpr int BN = 256;                        // UMMA N = columns of one accumulator
+    static constexpr int BN = BNV;                        // UMMA N = columns of one accumulator (64: small problems)
     static constexpr int BN_TILE = BN * NACC;             // columns of one tile (NACC accumulators share each A tile)
     static constexpr int BN_LOAD = BN_TILE / CTAS;        // columns of B this CTA loads per stage
     static constexpr int BK = 128 / ELEM;                 // one 128-byte swizzle row of K
@@ -388,11 +389,13 @@ __device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmPara
             if (J.notify != nullptr && atomicAdd(f.job_done + job, count) + count == job_batches) {
                 __threadfence_system();
                 st_release_sys(J.notify, f.epoch);
+                if (p.stats != nullptr) atomicMax(p.stats + 24 + min(J.panel, 7u), (unsigned long long)global_timer_ns());
             }
         } else {
             if (J.publish && atomicAdd(f.published + J.panel, count) + count == f.pub_need[J.panel]) {
                 __threadfence_system();
                 st_release_sys(f.pub_flags + J.panel, f.epoch);
+                if (p.stats != nullptr) p.stats[24 + min(J.panel, 7u)] = global_timer_ns();
             }
             if (atomicAdd(f.arrived + J.panel, count) + count == f.need[J.panel]) {
                 __threadfence();
@@ -484,6 +487,7 @@ struct Courier {
             if (state == 0) return;              // not yet: the caller has other things to look at
             (void)ld_acquire_sys(J.gate);        // every lane orders its own loads of the piece after the flag
             gate_open = true;
+            if (p.stats != nullptr && J.rows == 0 && lane == 0) p.stats[24 + min(J.panel, 7u)] = global_timer_ns();
         }
         const uint32_t g0 = (cur - job_first) * FETCH_UNROLL;
         uint32_t row = g0 / (spr ? spr : 1u), cs = g0 - row * spr;
@@ -506,13 +510,13 @@ struct Courier {
     }
 };
 
-template <int KIND, int CTAS, int NACC, int FETCH>
-__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH>::THREADS, 1)
+template <int KIND, int CTAS, int NACC, int FETCH, int BNV = 256>
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH, BNV>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmC, const GemmParams p,
                     const FetchParams f) {
-    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH>;
+    using Cfg = GemmCfg<KIND, CTAS, NACC, FETCH, BNV>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
@@ -563,6 +567,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     if constexpr (CTAS == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // 3xTF32: the pass that wrote the operand planes may still be running (programmatic dependent launch)
+    if constexpr (KIND == 1) griddep_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer

@@ -21,6 +21,13 @@
 
 namespace dxb {
 
+// Programmatic dependent launch: the tensor-core kernel that consumes the planes may be launched with the
+// "programmatic stream serialization" attribute.  Its CTAs then become resident once every CTA of the pass has
+// executed this instruction (or exited) and set up their barriers and tensor memory while the pass still runs;
+// they read the planes only after their own griddepcontrol.wait, which returns when the whole pass has completed
+// and its writes are visible.  Without that attribute on the next launch this is a no-op.
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float rn_tf32(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -40,38 +47,64 @@ __device__ __forceinline__ void split1(float x, float& hi, float& lo) {
 
 // X: rows x cols (ldx floats per row)  ->  hi, lo: rows x cols (ldw floats per row, ldw % 4 == 0,
 // planes 16-byte aligned).  One thread per group of 4 columns.
-__global__ void split_tf32_kernel(const float* __restrict__ X, uint64_t ldx, uint32_t rows, uint32_t cols,
-                                  float* __restrict__ hi, float* __restrict__ lo, uint64_t ldw, int vec_ok) {
+struct SplitJob {
+    const float* X;
+    uint64_t ldx;
+    uint32_t rows, cols;
+    float *hi, *lo;
+    uint64_t ldw;
+    int vec_ok;
+};
+
+__device__ __forceinline__ void split_group(const SplitJob& j, uint64_t i, uint32_t groups) {
+    const uint32_t r = uint32_t(i / groups);
+    const uint32_t c = uint32_t(i % groups) * 4;
+    const float* src = j.X + r * j.ldx + c;
+    float4 v;
+    if (j.vec_ok && c + 4 <= j.cols) {
+        v = __ldg(reinterpret_cast<const float4*>(src));
+    } else {
+        v.x = (c + 0 < j.cols) ? src[0] : 0.f;
+        v.y = (c + 1 < j.cols) ? src[1] : 0.f;
+        v.z = (c + 2 < j.cols) ? src[2] : 0.f;
+        v.w = (c + 3 < j.cols) ? src[3] : 0.f;
+    }
+    float4 h, l;
+    split1(v.x, h.x, l.x);
+    split1(v.y, h.y, l.y);
+    split1(v.z, h.z, l.z);
+    split1(v.w, h.w, l.w);
+    *reinterpret_cast<float4*>(j.hi + r * j.ldw + c) = h;
+    *reinterpret_cast<float4*>(j.lo + r * j.ldw + c) = l;
+}
+
+static __global__ void split_tf32_kernel(const float* __restrict__ X, uint64_t ldx, uint32_t rows, uint32_t cols,
+                                         float* __restrict__ hi, float* __restrict__ lo, uint64_t ldw, int vec_ok) {
+    allow_dependent_launch();
+    const SplitJob j{X, ldx, rows, cols, hi, lo, ldw, vec_ok};
     const uint32_t groups = (cols + 3) / 4;
     const uint64_t total = uint64_t(rows) * groups;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
-         i += uint64_t(gridDim.x) * blockDim.x) {
-        const uint32_t r = uint32_t(i / groups);
-        const uint32_t c = uint32_t(i % groups) * 4;
-        const float* src = X + r * ldx + c;
-        float4 v;
-        if (vec_ok && c + 4 <= cols) {
-            v = __ldg(reinterpret_cast<const float4*>(src));
-        } else {
-            v.x = (c + 0 < cols) ? src[0] : 0.f;
-            v.y = (c + 1 < cols) ? src[1] : 0.f;
-            v.z = (c + 2 < cols) ? src[2] : 0.f;
-            v.w = (c + 3 < cols) ? src[3] : 0.f;
-        }
-        float4 h, l;
-        split1(v.x, h.x, l.x);
-        split1(v.y, h.y, l.y);
-        split1(v.z, h.z, l.z);
-        split1(v.w, h.w, l.w);
-        *reinterpret_cast<float4*>(hi + r * ldw + c) = h;
-        *reinterpret_cast<float4*>(lo + r * ldw + c) = l;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x)
+        split_group(j, i, groups);
+}
+
+// Both operands of one product in ONE launch (small problems are launch-bound: 1024^3 spends more time between
+// kernels than inside them).
+static __global__ void split_tf32_pair_kernel(SplitJob a, SplitJob b) {
+    allow_dependent_launch();
+    const uint32_t ga = (a.cols + 3) / 4, gb = (b.cols + 3) / 4;
+    const uint64_t ta = uint64_t(a.rows) * ga, total = ta + uint64_t(b.rows) * gb;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        if (i < ta) split_group(a, i, ga);
+        else split_group(b, i - ta, gb);
     }
 }
 
 // B: K x N complex (ldb complex elements per row) -> hi, lo: 2K x 2N floats (ldw floats per row).
 // One thread per pair of complex columns (4 output floats per output row).
-__global__ void expand_split_cplx_b_kernel(const float2* __restrict__ B, uint64_t ldb, uint32_t K, uint32_t N,
+static __global__ void expand_split_cplx_b_kernel(const float2* __restrict__ B, uint64_t ldb, uint32_t K, uint32_t N,
                                            float* __restrict__ hi, float* __restrict__ lo, uint64_t ldw) {
+    allow_dependent_launch();
     const uint32_t groups = (N + 1) / 2;
     const uint64_t total = uint64_t(K) * groups;
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;

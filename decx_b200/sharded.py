@@ -378,11 +378,12 @@ class ShardedGemm:
     def fetch_stats(self):
         """Timing record of the last fused launch on this rank (after a synchronize), in microseconds relative
         to the kernel's start: when each panel was complete, kernel duration, total loader wait."""
-        if self.overlap != "fused" or not self._jobs or not self._pulls:
+        if self.overlap != "fused" or not self._jobs:
             return None
         w = self._fetch_scratch[256:512].view(torch.int64).cpu().tolist()
         t0 = w[16]
-        return {"panel_ready_us": [round((w[i] - t0) / 1e3, 1) for i in range(len(self.panels))],
+        return {"panel_ready_us": [round((w[i] - t0) / 1e3, 1) if w[i] else None for i in range(len(self.panels))],
+                "scatter_piece_us": [round((w[24 + i] - t0) / 1e3, 1) if w[24 + i] else None for i in range(min(8, len(self.panels)))],
                 "kernel_us": round((w[17] - t0) / 1e3, 1), "loader_wait_us_sum": round(w[18] / 1e3, 1),
                 "loader_waits": w[19]}
 
