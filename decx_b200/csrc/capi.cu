@@ -558,7 +558,10 @@ int host_path(int dev, HostPath*& hp) {
 // rows of A / D handled per pipeline step of the host-pointer path
 uint32_t host_block_rows(uint32_t M) {
     if (M <= 2048) return M;
-    uint32_t rb = uint32_t(round_up((uint64_t(M) + 7) / 8, 256));   // about 8 steps, whole 256-row tiles
+    // About 32 steps of whole 256-row tiles.  The copies, not the GEMMs, set the pace of this path, and what cannot
+    // overlap is the first block's upload and the last block's GEMM + download: small blocks keep both short
+    // (fp16 65536 x 16384 x 16384: 8 blocks left 8.5 ms of tail behind the last upload, 32 blocks leave 2 ms).
+    uint32_t rb = uint32_t(round_up((uint64_t(M) + 31) / 32, 256));
     if (rb < 1024) rb = 1024;
     return rb > M ? M : rb;
 }
@@ -905,7 +908,10 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
         if (uint64_t(j.row0) + j.rows > K) return DECXB200_EINVAL;
         if (j.rows != 0 && (j.src == nullptr || !aligned16(j.src))) return DECXB200_EINVAL;
         if (j.rows == 0 && j.gate == nullptr) return DECXB200_EINVAL;     // a piece nobody delivers and nobody flags
-        if (j.dst != nullptr && (j.rows == 0 || !aligned16(j.dst) || j.publish)) return DECXB200_EINVAL;
+        if (j.dst != nullptr && (j.rows == 0 || !aligned16(j.dst) || (j.publish != 0 && j.publish != DECXB200_FETCH_MULTICAST)))
+            return DECXB200_EINVAL;
+        if (j.dst == nullptr && j.publish > 1) return DECXB200_EINVAL;
+        if (j.publish == DECXB200_FETCH_MULTICAST && j.notify == nullptr) return DECXB200_EINVAL;
         if (j.dst == nullptr && j.notify != nullptr) return DECXB200_EINVAL;
         FetchJob& t = table[i];
         t.src = static_cast<const uint8_t*>(j.src);
@@ -915,7 +921,7 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
         t.row0 = j.row0; t.rows = j.rows;
         t.byte0 = j.col0 * 2; t.bytes = j.cols * 2;
         t.panel = j.panel;
-        t.publish = j.publish ? 1u : 0u;
+        t.publish = j.dst != nullptr ? j.publish : (j.publish ? 1u : 0u);
         const uint32_t nb = fetch_job_batches(t.rows, t.bytes);
         if (t.dst == nullptr) {
             f.need[t.panel] += nb;

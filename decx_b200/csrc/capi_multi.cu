@@ -29,7 +29,10 @@ struct Plan {
 
 uint32_t block_rows(uint32_t rows) {
     if (rows <= 2048) return rows;
-    uint32_t rb = uint32_t(round_up((uint64_t(rows) + 3) / 4, 256));     // about four steps, whole 256-row tiles
+    // about eight steps of whole 256-row tiles, 1024 rows or more: what cannot overlap the copies is the last
+    // block's GEMM and download
+    uint32_t rb = uint32_t(round_up((uint64_t(rows) + 7) / 8, 256));
+    if (rb < 1024) rb = 1024;
     return rb > rows ? rows : rb;
 }
 

@@ -120,6 +120,9 @@ struct GemmParams {
 //   push  (dst = another GPU's replica, src local): when the whole job is stored, `notify` -- a word in the TARGET's
 //         memory, its publish flag for the panel -- is set to the epoch.  Stores over NVLink are posted: no
 //         request has to travel towards the sender, whose inbound link may be busy receiving D.
+//         With publish == FETCH_MULTICAST both `dst` and `notify` are addresses in an NVLink multicast mapping of
+//         the replicas and their flags: every store is replicated by the switch into all bound GPUs, so the owner
+//         sends B over its link ONCE and no GPU has to fetch pieces from another.
 // rows == 0 is a piece something else delivers (a pushing GPU, a copy engine): the courier only waits for its gate
 // and counts it.
 struct FetchJob {
@@ -130,8 +133,10 @@ struct FetchJob {
     uint32_t row0, rows;
     uint32_t byte0, bytes;     // bytes % 16 == 0
     uint32_t panel;            // column panel the piece belongs to
-    uint32_t publish;          // pull jobs: 1 = other GPUs fetch this piece from here once it has landed (pub_flags)
+    uint32_t publish;          // pull jobs: 1 = other GPUs fetch this piece from here once it has landed (pub_flags);
+                               // push jobs: FETCH_MULTICAST = dst / notify are multicast addresses
 };
+constexpr uint32_t FETCH_MULTICAST = 2;
 constexpr uint32_t FETCH_UNROLL = 16;                   // 512-byte segments per batch (one warp, one go): 8 KB
 __host__ __device__ inline uint32_t fetch_job_batches(uint32_t rows, uint32_t bytes) {
     const uint64_t segs = uint64_t(rows) * ((bytes + 511u) / 512u);
@@ -388,7 +393,8 @@ __device__ __forceinline__ void fetch_flush(const FetchParams& f, const GemmPara
         if (push) {
             if (J.notify != nullptr && atomicAdd(f.job_done + job, count) + count == job_batches) {
                 __threadfence_system();
-                st_release_sys(J.notify, f.epoch);
+                if (J.publish == FETCH_MULTICAST) multimem_red_max_release_sys(J.notify, f.epoch);
+                else st_release_sys(J.notify, f.epoch);
                 if (p.stats != nullptr) atomicMax(p.stats + 24 + min(J.panel, 7u), (unsigned long long)global_timer_ns());
             }
         } else {
@@ -502,9 +508,15 @@ struct Courier {
             if (++cs == spr) { cs = 0; ++row; }
         }
         uint8_t* const dst = J.dst != nullptr ? J.dst : f.dst;
+        if (J.dst != nullptr && J.publish == FETCH_MULTICAST) {
 #pragma unroll
-        for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
-            if (off[u] != ~0ull) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+            for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
+                if (off[u] != ~0ull) multimem_st_v4(dst + off[u], v[u]);
+        } else {
+#pragma unroll
+            for (uint32_t u = 0; u < FETCH_UNROLL; ++u)
+                if (off[u] != ~0ull) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+        }
         ++pend;
         holding = false;
     }

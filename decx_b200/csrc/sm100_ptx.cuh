@@ -53,6 +53,17 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Stores through an NVLink multicast address: NVSwitch writes the value into the same offset of every GPU bound to
+// the multicast object, so one store over this GPU's link reaches all of them.
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// Raises a flag word in every bound GPU's memory to at least `v` (flags only grow: they hold step epochs); release:
+// ordered after this thread's earlier writes and fences.
+__device__ __forceinline__ void multimem_red_max_release_sys(unsigned* mc, unsigned v) {
+    asm volatile("multimem.red.release.sys.global.max.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
 // 16 bytes that another GPU or a copy engine may have written since this SM last read them: never from L1
 __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
     uint4 v;

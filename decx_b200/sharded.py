@@ -131,7 +131,7 @@ def row_pieces(K, parts, align=16):
     return out
 
 
-def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr, scatter="push"):
+def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr, scatter="push", mc_ptr=None, mc_pub_ptr=None):
     """Job list of `rank` for the fused kernel, as tuples
     (src, gate, row0, rows, col0, cols, panel, publish, dst, notify).
 
@@ -142,10 +142,19 @@ def fetch_jobs(rank, owner, active, K, panels, b_ptr, pub_ptr, scatter="push"):
           publish flag (posted stores: no request travels towards the owner, whose inbound link carries D); the
           holder lists the piece as a rows == 0 job gated on its own flag;
       scatter="pull": the holder's couriers read it from the owner's B and publish it themselves.
+      scatter="multicast": no pieces at all.  The owner's couriers store every panel ONCE through the NVLink
+          multicast mapping of the replicas (mc_ptr) and raise everybody's publish flag through the multicast
+          mapping of the flags (mc_pub_ptr); every other rank lists one rows == 0 job per panel gated on its own flag.
     b_ptr[r] / pub_ptr[r]: address of rank r's replica of B / of its publish flags, as this rank maps them."""
     holders = [r for r in active if r != owner]
     if rank not in active or not holders:
         return []
+    if scatter == "multicast":
+        if not mc_ptr or not mc_pub_ptr:
+            raise ValueError("multicast scatter needs the multicast addresses of the replica and of the flags")
+        if rank == owner:
+            return [(b_ptr[owner], None, 0, K, c0, w, p, 2, mc_ptr, mc_pub_ptr + 4 * p) for p, (c0, w) in enumerate(panels)]
+        return [(None, pub_ptr[rank] + 4 * p, 0, 0, c0, w, p, 0, None, None) for p, (c0, w) in enumerate(panels)]
     pieces = row_pieces(K, len(holders))
     jobs = []
     if rank == owner:
@@ -339,6 +348,13 @@ class ShardedGemm:
             words.zero_()
             self.flags, self.pub_flags = words[:16], words[16:32]
             self._pub_ptrs = [p + n * self._esz_of(self.dtype) + 64 for p in self._bptrs]
+            mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+            self._mc_ptr = mc or None
+            self._mc_pub_ptr = (mc + n * self._esz_of(self.dtype) + 64) if mc else None
+            if self._scatter == "multicast" and not mc:
+                print("decx_b200.sharded: no NVLink multicast mapping for the replica; the owner pushes piece by piece",
+                      file=sys.stderr)
+                self._scatter = "push"
             return True
         except Exception as e:
             print(f"decx_b200.sharded: symmetric memory unavailable ({type(e).__name__}: {e}); copy-engine delivery",
@@ -354,7 +370,7 @@ class ShardedGemm:
         capi = self._capi
         active = [r for r, (_, n) in enumerate(self.rows) if n > 0]
         tuples = fetch_jobs(self.rank, self.owner, active, self.K, self.panels, self._bptrs, self._pub_ptrs,
-                            scatter=self._scatter)
+                            scatter=self._scatter, mc_ptr=self._mc_ptr, mc_pub_ptr=self._mc_pub_ptr)
         self._jobs = [capi.fetch_job(*t) for t in tuples]
         self._pulls = any(t[8] is None for t in tuples)
         need = int(capi.lib.decxb200_fetch_scratch_bytes(max(len(self._jobs), 1)))

@@ -304,6 +304,12 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
  *   owner -- whose inbound link is busy receiving D -- scatters B by pushing, and the receivers list the pushed
  *   piece as a rows == 0 job gated on their own publish flag.  A GPU whose jobs all push (the owner) passes NULL
  *   for ready_flags / pub_flags and runs ungated.
+ *   With publish = DECXB200_FETCH_MULTICAST a push job's dst and notify are addresses inside an NVLink MULTICAST
+ *   mapping of all the GPUs' replicas and flag words (what CUDA's multicast objects / torch symmetric memory's
+ *   multicast_ptr provide): the couriers store with multimem.st, the switch writes every store into all bound
+ *   GPUs, and the flag of every GPU is raised with one multimem.red (max).  The owner then sends B over its link
+ *   once, nobody fetches pieces from anybody, and the receivers' job lists hold only rows == 0 jobs gated on
+ *   their own flags.
  *   jobs:      HOST array, copied by the call.  gate == NULL: the source is readable now.  rows == 0: a piece
  *              that something else writes into the replica (a copy engine); the courier only waits for its
  *              gate and counts it.  Every panel needs at least one job.  col0, cols: multiples of 8.
@@ -316,6 +322,7 @@ DECXB200_API int decxb200_gemm_fp16_panels(void* stream, uint32_t M, uint32_t N,
  *   All waits are bounded: status 0x106 (a panel never completed) or 0x107 (a gate never opened).
  *   Epochs must increase from one use of the flags to the next.
  */
+#define DECXB200_FETCH_MULTICAST 2
 typedef struct decxb200_fetch_job {
     const void* src;
     const unsigned* gate;
@@ -324,7 +331,7 @@ typedef struct decxb200_fetch_job {
     uint32_t row0, rows;
     uint32_t col0, cols;
     uint32_t panel;
-    uint32_t publish;
+    uint32_t publish;          /* pull jobs: 0 / 1; push jobs: 0 or DECXB200_FETCH_MULTICAST */
 } decxb200_fetch_job;
 DECXB200_API size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs);
 DECXB200_API int decxb200_gemm_fp16_fetch(void* stream, uint32_t M, uint32_t N, uint32_t K,

@@ -165,3 +165,24 @@ def test_fetch_jobs_cover_b_exactly_once_and_gate_on_the_publisher():
                         src_rank = b_ptr.index(j[SRC])
                         assert j[GATE] == pub_ptr[src_rank] + 4 * j[P] and j[PUB] == 0
                         assert held[(src_rank, j[P])] == (j[R0], j[NR])
+
+
+def test_multicast_jobs_one_store_job_per_panel_on_the_owner():
+    from decx_b200.sharded import fetch_jobs, fetch_panel_plan
+    K, N = 2053, 2104
+    panels = fetch_panel_plan(N)
+    SRC, GATE, R0, NR, C0, W, P, PUB, DST, NOTIFY = range(10)
+    world, owner, active = 4, 1, [0, 1, 3]
+    b_ptr = [1000 * (r + 1) for r in range(world)]
+    pub_ptr = [50 + 1000 * (r + 1) for r in range(world)]
+    with pytest.raises(ValueError):
+        fetch_jobs(owner, owner, active, K, panels, b_ptr, pub_ptr, "multicast")
+    jobs = fetch_jobs(owner, owner, active, K, panels, b_ptr, pub_ptr, "multicast", mc_ptr=9000, mc_pub_ptr=9050)
+    assert len(jobs) == len(panels)
+    for p, ((c0, w), j) in enumerate(zip(panels, jobs)):
+        assert (j[SRC], j[GATE], j[R0], j[NR], j[C0], j[W], j[P]) == (b_ptr[owner], None, 0, K, c0, w, p)
+        assert j[PUB] == 2 and j[DST] == 9000 and j[NOTIFY] == 9050 + 4 * p
+    for r in (0, 3):
+        jobs = fetch_jobs(r, owner, active, K, panels, b_ptr, pub_ptr, "multicast", mc_ptr=9000, mc_pub_ptr=9050)
+        assert [(j[NR], j[GATE], j[P], j[DST]) for j in jobs] == [(0, pub_ptr[r] + 4 * p, p, None) for p in range(len(panels))]
+    assert fetch_jobs(2, owner, active, K, panels, b_ptr, pub_ptr, "multicast", mc_ptr=9000, mc_pub_ptr=9050) == []

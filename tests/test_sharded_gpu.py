@@ -24,7 +24,8 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, dtype_name, gather, bcast, out, overlap=None, tile=0, expect_overlap=None):
+def _worker(rank, world, port, M, N, K, dtype_name, gather, bcast, out, overlap=None, tile=0, expect_overlap=None,
+            scatter="push"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -42,7 +43,7 @@ def _worker(rank, world, port, M, N, K, dtype_name, gather, bcast, out, overlap=
             mk = lambda r, c: (torch.rand((r, c), device=dev, generator=g) * 2 - 1).to(dtype)
         A, B = mk(M, K), mk(K, N)                     # same seed on every rank: identical full inputs
         sg = ShardedGemm(M, N, K, dtype, owner=0, panels=3 if overlap != "fused" else "ramp", gather=gather, device=dev,
-                         bcast=bcast, overlap=overlap, tile=tile)
+                         bcast=bcast, overlap=overlap, tile=tile, scatter=scatter)
         if expect_overlap is not None:
             assert sg.overlap == expect_overlap, (sg.overlap, expect_overlap)
         sg.A.copy_(A[sg.row0:sg.row0 + sg.nrows])
@@ -101,20 +102,26 @@ FUSED_CASES = [
     ((2048, 4096, 2048), "fused", 3, "fused"),
     ((2048, 4096, 2048), "single", 3, "single"),     # copy-engine delivery + flag-gated wide tile
     ((520, 1024, 256), None, 0, "fused"),            # fewer row blocks than ranks can occur at 4 GPUs
+    ((1300, 2104, 2304), None, 3, "fused", "pull"),       # receivers load their pieces from the owner
+    ((1300, 2104, 2304), None, 3, "fused", "multicast"),  # the owner stores through the NVLink multicast mapping
+    ((2048, 4096, 2048), "fused", 0, "fused", "multicast"),
 ]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("shape,overlap,tile,expect", FUSED_CASES)
-def test_fp16_single_launch_paths_equal_single_gpu(shape, overlap, tile, expect):
+@pytest.mark.parametrize("case", FUSED_CASES)
+def test_fp16_single_launch_paths_equal_single_gpu(case):
     """fp16 with the broadcast of B inside the step's one launch: the kernel-fetched ("fused") and the
     copy-engine-fed ("single") forms, also on the 256 x 512 tile the large configurations run."""
+    shape, overlap, tile, expect = case[:4]
+    scatter = case[4] if len(case) > 4 else "push"
     world = min(torch.cuda.device_count(), 4)
     M, N, K = shape
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, "float16", "peer", "p2p", q, overlap, tile, expect))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, "float16", "peer", "p2p", q, overlap, tile, expect,
+                                               scatter))
              for r in range(world)]
     for p in procs:
         p.start()
