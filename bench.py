@@ -288,7 +288,7 @@ def time_aux(torch, name, device, iters=10, warmup=3):
         C, n, k = ex["C"], ex["n"], ex["k"]
         src, ker = rnd((rows, cols, C), tdt), rnd((n, k, k, C), tdt)
         out = Bl.conv2d(src, ker, (1, 1), 2)
-        need = int(capi_lib().decxb200_conv2d_fp32_workspace_bytes(rows, cols, C, k, k, n, 1, 1, 2, 0))
+        need = int(capi_lib().decxb200_conv2d_fp32_workspace_bytes(rows, cols, C, k, k, n, 1, 1, 2, 0, 0))
         ws = torch.empty(need, dtype=torch.uint8, device=device)
         run = lambda: Bl.conv2d(src, ker, (1, 1), 2, out=out, workspace=ws)
         work, unit, bound = 2 * rows * cols * k * k * C * n, "TFLOP/s", "tensor (3xTF32) behind an HBM-bound im2col pass"

@@ -95,7 +95,9 @@ def conv2d(src, kernels, strides=(1, 1), extend=0, out=None, workspace=None, sta
     src_dp, src_wp = src.stride(1), src.stride(0) // src.stride(1)
     k_dp, k_wp = kernels.stride(2), kernels.stride(1) // kernels.stride(2)
     dst_dp, dst_wp = out.stride(1), out.stride(0) // out.stride(1)
-    need = int(capi.lib.decxb200_conv2d_fp32_workspace_bytes(H, W, C, kh, kw, n, sx, sy, extend, dst_wp))
+    # an odd pitch in the query selects the form that works for every destination
+    need = int(capi.lib.decxb200_conv2d_fp32_workspace_bytes(H, W, C, kh, kw, n, sx, sy, extend, dst_wp,
+                                                             dst_dp if out.data_ptr() % 16 == 0 else 1))
     if workspace is None or workspace.numel() < need:
         workspace = torch.empty(need, dtype=torch.uint8, device=src.device)
     with torch.cuda.device(src.device):

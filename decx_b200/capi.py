@@ -82,7 +82,7 @@ def _load():
     lib.decxb200_conv2d_fp32_out_dims.restype = ci
     lib.decxb200_conv2d_fp32_out_dims.argtypes = [u32, u32, u32, u32, u32, u32, ci, ctypes.POINTER(u32), ctypes.POINTER(u32)]
     lib.decxb200_conv2d_fp32_workspace_bytes.restype = sz
-    lib.decxb200_conv2d_fp32_workspace_bytes.argtypes = [u32, u32, u32, u32, u32, u32, u32, u32, ci, u32]
+    lib.decxb200_conv2d_fp32_workspace_bytes.argtypes = [u32, u32, u32, u32, u32, u32, u32, u32, ci, u32, u32]
     lib.decxb200_conv2d_fp32.restype = ci
     lib.decxb200_conv2d_fp32.argtypes = [vp, vp, u32, u32, u32, u32, u32, vp, u32, u32, u32, u32, u32, u64, vp, u32, u32,
                                          u32, u32, ci, vp, sz, vp]

@@ -133,14 +133,18 @@ int make_map_b_chunked(CUtensorMap* map, bool f16, const void* base, uint64_t ro
 
 template <int KIND, int CTAS, int NACC = 1, int FETCH = 0, int BNV = 256>
 int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                const CUtensorMap& b1, GemmParams p, int max_ctas, const FetchParams* fetch = nullptr, bool pdl = false) {
+                const CUtensorMap& b1, GemmParams p, int max_ctas, const FetchParams* fetch = nullptr, bool pdl = false,
+                const CUtensorMap* dmap_given = nullptr) {
     // D through TMA bulk stores (staged in shared memory, 128-byte rows) whenever its rows are 16-byte aligned:
     // that is what makes the stores efficient when D lives in another GPU's memory; DECXB200_TMA_STORE=0 disables
     static const int tma_store_env = [] { const char* e = getenv("DECXB200_TMA_STORE"); return e ? atoi(e) : 1; }();
     CUtensorMap dmap = a0, cmap = a0;
     p.d_tma = 0;
     p.c_tma = 0;
-    if (tma_store_env && p.vec_d) {
+    if (dmap_given != nullptr) {            // the caller built the map of D itself (convolution: a 3-D map)
+        dmap = *dmap_given;
+        p.d_tma = 1;
+    } else if (tma_store_env && p.vec_d) {
         const bool f16 = (KIND == 0);
         if (make_map(&dmap, f16, p.D, p.M, p.N, p.ldd, f16 ? 64 : 32, 32) == 0) p.d_tma = 1;
         // C through the same staging tile (TMA load, same box and swizzle) when its rows are 16-byte aligned too
@@ -620,6 +624,70 @@ int dxb_host::gemm_tf32_planes(cudaStream_t stream, uint32_t M, uint32_t N, uint
     if (dev < 0 || dev >= MAX_DEVICES) return DECXB200_EINVAL;
     return run_tf32(stream, dev, false, M, N, K, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, nullptr, 0, D, ldd, Scalars(), status,
                     default_cta_group(), 0);
+}
+
+// Implicit-GEMM convolution on zero-bordered tf32 planes of the source (see GemmParams::conv_tw).
+int dxb_host::conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsigned* status) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return DECXB200_EDRIVER;
+    int dev = 0;
+    const cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return int(ce);
+    if (dev < 0 || dev >= MAX_DEVICES) return DECXB200_EINVAL;
+    if (c.tw != 32 && c.tw != 64 && c.tw != 128) return DECXB200_EINVAL;
+    const uint32_t th = 128 / c.tw;
+    const uint32_t tiles_x = (c.OW + c.tw - 1) / c.tw, tiles_y = (c.OH + th - 1) / th;
+    const uint32_t row_floats = c.kw * c.Cp;                       // contiguous floats of one kernel row at one x
+    const uint32_t kbi = (row_floats + 31) / 32;
+    CUtensorMap a[2], d;
+    for (int pl = 0; pl < 2; ++pl) {
+        // (k in kernel row, x, i, y): x advances sx pixels, i one source row, y sy source rows
+        cuuint64_t dims[4] = {row_floats, c.OW, c.kh, c.OH};
+        cuuint64_t strides[3] = {uint64_t(c.sx) * c.Cp * 4, uint64_t(c.Wp) * c.Cp * 4, uint64_t(c.sy) * c.Wp * c.Cp * 4};
+        cuuint32_t box[4] = {32, c.tw, 1, th};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        const CUresult r = enc(&a[pl], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(pl == 0 ? c.src_hi : c.src_lo),
+                               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return DECXB200_EDRIVER;
+    }
+    {
+        cuuint64_t dims[3] = {c.n, c.OW, c.OH};
+        cuuint64_t strides[2] = {uint64_t(c.dst_dpitch) * 4, uint64_t(c.dst_wpitch) * c.dst_dpitch * 4};
+        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        const CUresult r = enc(&d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, c.dst, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return DECXB200_EDRIVER;
+    }
+    GemmParams p;
+    fill_common(p, Scalars(), nullptr, c.dst, status);
+    p.M = tiles_x * tiles_y * 128;                                  // every tile row exists; TMA clips at OW / OH
+    p.N = c.n;
+    p.K = c.kh * kbi * 32;
+    p.ldd = c.dst_dpitch;
+    p.epi_mode = EPI_REAL;
+    p.vec_d = 1;
+    p.conv_tw = c.tw;
+    p.conv_tiles_x = tiles_x;
+    p.conv_kbi = kbi;
+    p.b_chunked_map = 1;
+    const bool narrow = c.n <= 128;
+    const uint32_t chunks = narrow ? GemmCfg<1, 1, 1, 0, 64>::B_CHUNKS : GemmCfg<1, 1>::B_CHUNKS;
+    using C1 = GemmCfg<1, 1>;
+    CUtensorMap b0, b1;
+    int rc;
+    if ((rc = make_map_b_chunked(&b0, false, c.b_hi, p.K, c.n, c.ldbw, C1::CHUNK_N, C1::BK, chunks,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+        return rc;
+    if ((rc = make_map_b_chunked(&b1, false, c.b_lo, p.K, c.n, c.ldbw, C1::CHUNK_N, C1::BK, chunks,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
+        return rc;
+    rc = narrow ? launch_gemm<1, 1, 1, 0, 64>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
+                : launch_gemm<1, 1>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    if (rc == 0) t_variant += 20000;
+    return rc;
 }
 
 extern "C" {

@@ -234,13 +234,50 @@ int decxb200_conv2d_fp32_out_dims(uint32_t H, uint32_t W, uint32_t kh, uint32_t 
     return 0;
 }
 
+namespace {
+// which form a convolution takes, and what each needs
+struct ConvPlan {
+    bool implicit;
+    uint32_t tw, Hp, Wp, kbi;
+    uint64_t M, ldaw, ldbw, Kb;            // materialised: rows of the im2col matrix, its pitch; both: B's pitch and rows
+    uint64_t a_bytes, b_bytes;             // per plane
+};
+ConvPlan conv_plan(const Conv2dGeom& g, uint32_t n_kernels, uint32_t dst_dpitch) {
+    static const int implicit_env = [] { const char* e = getenv("DECXB200_CONV_IMPLICIT"); return e ? atoi(e) : 1; }();
+    ConvPlan p;
+    memset(&p, 0, sizeof(p));
+    p.ldbw = round_up(n_kernels, 32);
+    p.implicit = implicit_env != 0 && (n_kernels % 4) == 0 && (dst_dpitch % 4) == 0;
+    if (p.implicit) {
+        // tile row width: least padding of the output columns, wider on ties
+        uint64_t best = ~0ull;
+        for (uint32_t tw : {128u, 64u, 32u}) {
+            const uint32_t th = 128 / tw;
+            const uint64_t cover = uint64_t((g.OW + tw - 1) / tw) * tw * ((g.OH + th - 1) / th) * th;
+            if (cover < best) { best = cover; p.tw = tw; }
+        }
+        p.Hp = (g.OH - 1) * g.sy + g.kh;
+        p.Wp = (g.OW - 1) * g.sx + g.kw;
+        p.kbi = (g.kw * g.Cp + 31) / 32;
+        p.Kb = uint64_t(g.kh) * p.kbi * 32;
+        p.a_bytes = round_up(uint64_t(p.Hp) * p.Wp * g.Cp * 4, 256);
+    } else {
+        p.M = uint64_t(g.OH) * g.dst_wpitch;
+        p.ldaw = round_up(g.Kc, 32);
+        p.Kb = g.Kc;
+        p.a_bytes = round_up(p.M * p.ldaw * 4, 256);
+    }
+    p.b_bytes = round_up(p.Kb * p.ldbw * 4, 256);
+    return p;
+}
+}  // namespace
+
 size_t decxb200_conv2d_fp32_workspace_bytes(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint32_t kw, uint32_t n_kernels,
-                                            uint32_t sx, uint32_t sy, int extend, uint32_t dst_wpitch) {
+                                            uint32_t sx, uint32_t sy, int extend, uint32_t dst_wpitch, uint32_t dst_dpitch) {
     Conv2dGeom g;
     if (n_kernels == 0 || conv2d_geometry(H, W, C, kh, kw, sx, sy, extend, dst_wpitch, g) != 0) return 0;
-    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch;
-    const uint64_t a = round_up(M * round_up(g.Kc, 32) * 4, 256), b = round_up(uint64_t(g.Kc) * round_up(n_kernels, 32) * 4, 256);
-    return size_t(2 * a + 2 * b);
+    const ConvPlan p = conv_plan(g, n_kernels, dst_dpitch ? dst_dpitch : n_kernels);
+    return size_t(2 * p.a_bytes + 2 * p.b_bytes);
 }
 
 int decxb200_conv2d_fp32(void* stream_, const void* src, uint32_t H, uint32_t W, uint32_t C, uint32_t src_wpitch,
@@ -257,26 +294,42 @@ int decxb200_conv2d_fp32(void* stream_, const void* src, uint32_t H, uint32_t W,
         return DECXB200_EINVAL;
     g.src_wpitch = src_wpitch;
     g.src_dpitch = src_dpitch;
-    const size_t need = decxb200_conv2d_fp32_workspace_bytes(H, W, C, kh, kw, n_kernels, sx, sy, extend, dst_wpitch);
+    // a destination that is not 16-byte aligned takes the materialised form whatever its pitch
+    const ConvPlan p = conv_plan(g, n_kernels, aligned16(dst) ? dst_dpitch : 1);
+    const size_t need = size_t(2 * p.a_bytes + 2 * p.b_bytes);
     if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
         return DECXB200_EWORKSPACE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-    const uint64_t M = uint64_t(g.OH) * g.dst_wpitch, ldaw = round_up(g.Kc, 32), ldbw = round_up(n_kernels, 32);
-    const uint64_t a_bytes = round_up(M * ldaw * 4, 256), b_bytes = round_up(uint64_t(g.Kc) * ldbw * 4, 256);
     uint8_t* w = static_cast<uint8_t*>(workspace);
     float* a_hi = reinterpret_cast<float*>(w);
-    float* a_lo = reinterpret_cast<float*>(w + a_bytes);
-    float* b_hi = reinterpret_cast<float*>(w + 2 * a_bytes);
-    float* b_lo = reinterpret_cast<float*>(w + 2 * a_bytes + b_bytes);
+    float* a_lo = reinterpret_cast<float*>(w + p.a_bytes);
+    float* b_hi = reinterpret_cast<float*>(w + 2 * p.a_bytes);
+    float* b_lo = reinterpret_cast<float*>(w + 2 * p.a_bytes + p.b_bytes);
     const int vec = aligned16(src) && (src_dpitch % 4) == 0;
     auto blocks = [](uint64_t work) { return unsigned(work / 256 + 1 > 148ull * 32 ? 148ull * 32 : work / 256 + 1); };
-    im2col_split_kernel<<<blocks(M * g.kh * g.kw * (g.Cp / 4)), 256, 0, s>>>(static_cast<const float*>(src), a_hi, a_lo, ldaw,
-                                                                              g, vec);
-    pack_kernels_split_kernel<<<blocks(uint64_t(g.Kc) * ((n_kernels + 3) / 4)), 256, 0, s>>>(
-        static_cast<const float*>(kernels), kernel_stride, kernel_wpitch, kernel_dpitch, kh, kw, C, g.Cp, n_kernels, b_hi, b_lo,
-        ldbw);
-    if ((rc = last_error()) != 0) return rc;
-    rc = dxb_host::gemm_tf32_planes(s, uint32_t(M), n_kernels, g.Kc, a_hi, a_lo, ldaw, b_hi, b_lo, ldbw, dst, dst_dpitch, status);
+    const uint32_t row_pad = p.implicit ? p.kbi * 32 : g.kw * g.Cp;
+    pack_kernels_split_kernel<<<blocks(p.Kb * ((n_kernels + 3) / 4)), 256, 0, s>>>(
+        static_cast<const float*>(kernels), kernel_stride, kernel_wpitch, kernel_dpitch, kh, kw, C, g.Cp, n_kernels, row_pad,
+        b_hi, b_lo, p.ldbw);
+    if (p.implicit) {
+        pad_split_src_kernel<<<blocks(uint64_t(p.Hp) * p.Wp * (g.Cp / 4)), 256, 0, s>>>(static_cast<const float*>(src), a_hi,
+                                                                                        a_lo, p.Hp, p.Wp, g, vec);
+        if ((rc = last_error()) != 0) return rc;
+        dxb_host::ConvPlanes c;
+        memset(&c, 0, sizeof(c));
+        c.src_hi = a_hi; c.src_lo = a_lo; c.Wp = p.Wp; c.Cp = g.Cp;
+        c.b_hi = b_hi; c.b_lo = b_lo; c.ldbw = p.ldbw;
+        c.kh = kh; c.kw = kw; c.n = n_kernels; c.sx = sx; c.sy = sy; c.OH = g.OH; c.OW = g.OW;
+        c.dst = static_cast<float*>(dst); c.dst_wpitch = g.dst_wpitch; c.dst_dpitch = dst_dpitch;
+        c.tw = p.tw;
+        rc = dxb_host::conv_tf32_implicit(s, c, status);
+    } else {
+        im2col_split_kernel<<<blocks(p.M * g.kh * g.kw * (g.Cp / 4)), 256, 0, s>>>(static_cast<const float*>(src), a_hi, a_lo,
+                                                                                    p.ldaw, g, vec);
+        if ((rc = last_error()) != 0) return rc;
+        rc = dxb_host::gemm_tf32_planes(s, uint32_t(p.M), n_kernels, g.Kc, a_hi, a_lo, p.ldaw, b_hi, b_lo, p.ldbw, dst,
+                                        dst_dpitch, status);
+    }
     dxb_host::count_launch(2);
     return rc;
 }

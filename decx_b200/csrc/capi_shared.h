@@ -26,4 +26,17 @@ int gemm_tf32_planes(cudaStream_t stream, uint32_t M, uint32_t N, uint32_t K, co
                      uint64_t ldaw, const float* b_hi, const float* b_lo, uint64_t ldbw, void* D, uint64_t ldd,
                      unsigned* status);
 
+// fp32 convolution as an implicit GEMM: the kernel's operand tiles are TMA boxes of the zero-bordered source planes.
+struct ConvPlanes {
+    const float *src_hi, *src_lo;     // Hp x Wp x Cp each (Cp % 4 == 0), Hp >= (OH-1)*sy + kh, Wp >= (OW-1)*sx + kw
+    uint32_t Wp, Cp;
+    const float *b_hi, *b_lo;         // (kh * round_up(kw*Cp, 32)) x n, rows ldbw floats apart
+    uint64_t ldbw;
+    uint32_t kh, kw, n, sx, sy, OH, OW;
+    float* dst;                       // OH x OW x n, 16-byte aligned, dst_dpitch % 4 == 0, n % 4 == 0
+    uint32_t dst_wpitch, dst_dpitch;
+    uint32_t tw;                      // output positions of one tile row: 32, 64 or 128
+};
+int conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsigned* status);
+
 }  // namespace dxb_host

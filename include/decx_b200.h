@@ -239,9 +239,13 @@ DECXB200_API int decxb200_cast2d(int kind, void* stream, uint32_t rows, uint32_t
  *                                       (im2col_fp32.cu:132)
  * (the values of de::extend_label, srcs/includes/DECX/basic_proc/VectorProc.h:22-26).  kernels: n_kernels tensors of
  * kh x kw x C, tensor t at kernels + t * kernel_stride floats.  dst: OH x OW x n_kernels with dst_wpitch (0 = OW) and
- * dst_dpitch >= n_kernels; positions x in [OW, dst_wpitch) of every dst row are written with zeros.  All device
- * pointers; asynchronous on `stream`; workspace (256-byte aligned) holds the im2col matrix, the packed kernels and the
- * GEMM's tf32 planes.  The tensor containers (de::GPU_Tensor, de::GPU_TensorArray) are not part of this library: this
+ * dst_dpitch >= n_kernels; positions x in [OW, dst_wpitch) of the dst rows are left alone or written with zeros.
+ * All device pointers; asynchronous on `stream`.  Two forms: when n_kernels and dst_dpitch are multiples of 4 and dst
+ * is 16-byte aligned (DECX's tensors are) the GEMM kernel reads its operand tiles straight out of tf32 planes of the
+ * zero-bordered source with 4-D TMA boxes (implicit GEMM; workspace = those planes + the packed kernels, about twice
+ * the source); otherwise the tf32 planes of the im2col matrix are written to the workspace first.  The workspace
+ * query takes the destination pitch for that reason; a misaligned dst with a multiple-of-4 pitch needs the size the
+ * query returns for an odd pitch.  The tensor containers (de::GPU_Tensor, de::GPU_TensorArray) are not part of this library: this
  * entry point is what the reference's conv2D_im2col_fp32_caller would bind.
  */
 #define DECXB200_EXTEND_NONE 0
@@ -250,7 +254,7 @@ DECXB200_API int decxb200_conv2d_fp32_out_dims(uint32_t H, uint32_t W, uint32_t 
                                                int extend, uint32_t* OH, uint32_t* OW);
 DECXB200_API size_t decxb200_conv2d_fp32_workspace_bytes(uint32_t H, uint32_t W, uint32_t C, uint32_t kh, uint32_t kw,
                                                          uint32_t n_kernels, uint32_t sx, uint32_t sy, int extend,
-                                                         uint32_t dst_wpitch);
+                                                         uint32_t dst_wpitch, uint32_t dst_dpitch /* 0 = n_kernels */);
 DECXB200_API int decxb200_conv2d_fp32(void* stream, const void* src, uint32_t H, uint32_t W, uint32_t C,
                                       uint32_t src_wpitch, uint32_t src_dpitch,
                                       const void* kernels, uint32_t kh, uint32_t kw, uint32_t n_kernels,

@@ -55,8 +55,12 @@ def test_out_dims_and_argument_checks():
     assert f(2, 2, 3, 3, 1, 1, 0, ctypes.byref(oh), ctypes.byref(ow)) != 0          # kernel larger than the source
     assert f(8, 8, 3, 3, 1, 1, 1, ctypes.byref(oh), ctypes.byref(ow)) != 0          # reflect border: not in the reference either
     assert f(8, 8, 3, 3, 0, 1, 0, ctypes.byref(oh), ctypes.byref(ow)) != 0
-    assert capi.lib.decxb200_conv2d_fp32_workspace_bytes(8, 8, 4, 3, 3, 2, 1, 1, 0, 0) > 0
-    assert capi.lib.decxb200_conv2d_fp32_workspace_bytes(8, 8, 4, 3, 3, 0, 1, 1, 0, 0) == 0
+    assert capi.lib.decxb200_conv2d_fp32_workspace_bytes(8, 8, 4, 3, 3, 2, 1, 1, 0, 0, 0) > 0
+    assert capi.lib.decxb200_conv2d_fp32_workspace_bytes(8, 8, 4, 3, 3, 0, 1, 1, 0, 0, 0) == 0
+    # implicit form (planes of the bordered source) needs far less than the materialised im2col matrix
+    big = capi.lib.decxb200_conv2d_fp32_workspace_bytes(256, 256, 64, 3, 3, 64, 1, 1, 2, 0, 63 + 2)
+    small = capi.lib.decxb200_conv2d_fp32_workspace_bytes(256, 256, 64, 3, 3, 64, 1, 1, 2, 0, 64)
+    assert 0 < small < big // 4
     # no device work is reached with bad arguments
     assert capi.lib.decxb200_conv2d_fp32(None, None, 8, 8, 4, 8, 4, None, 3, 3, 2, 3, 4, 36, None, 0, 4, 1, 1, 0, None, 0,
                                          None) == -1
@@ -74,6 +78,11 @@ GPU_CASES = [
     ((128, 160, 32), (64, 3, 3), (1, 1), 0, (0, 0)),
     ((31, 29, 64), (128, 1, 1), (1, 1), 2, (0, 0)),         # pointwise
     ((40, 40, 4), (8, 11, 11), (4, 4), 2, (0, 0)),
+    ((33, 70, 8), (12, 3, 3), (1, 1), 2, (5, 4)),           # 64-wide tile rows, pitched destination
+    ((20, 300, 16), (260, 3, 5), (2, 1), 0, (0, 0)),        # more than 256 kernels: two tile columns of the wide tile
+    ((9, 9, 32), (4, 9, 9), (1, 1), 2, (0, 0)),             # kernel as large as the image
+    ((64, 64, 3), (16, 7, 7), (2, 2), 2, (0, 1)),           # RGB-like source, stride 2
+    ((17, 19, 20), (8, 2, 2), (1, 1), 0, (0, 0)),           # even kernel, kw * C not a multiple of 32
 ]
 
 
@@ -105,13 +114,17 @@ def test_conv2d_fp32(case):
     blas.conv2d(tsrc, tker, strides, extend, out=out, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+    from decx_b200 import capi
+    implicit = capi.lib.decxb200_last_kernel_variant() >= 20000
+    assert implicit == (n % 4 == 0 and (n + dextra) % 4 == 0)          # obuf is 16-byte aligned
     got = out.cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all()
     assert (np.abs(got - ref) <= 1e-5 * mag + 1e-30).all()
     full = obuf.cpu().numpy()
     assert np.isnan(full[:, :, n:]).all()                      # channel padding untouched
-    if wextra:
-        assert (full[:, OW:, :n] == 0).all()                    # row padding written with zeros, as documented
+    if wextra:                                                  # row padding: left alone (implicit) or zeros
+        pad = full[:, OW:, :n]
+        assert np.isnan(pad).all() if implicit else (pad == 0).all()
 
 
 @pytest.mark.gpu
