@@ -61,6 +61,7 @@ AUX = {
     # rows x cols = H x W of the source tensor; zero border, stride 1
     "conv2d_f32_512x512x64_k3_n128": ("conv", "float32", 512, 512, {"C": 64, "n": 128, "k": 3}),
 }
+DEFAULT_SCATTER = "push"
 FP64_NOMINAL_TFLOPS = 40.0      # B200 datasheet fp64 (vector and tensor); no measured fp64 peak exists for this pool
 
 ARITH = {"float16": "f16 (fp32 accumulate)", "float32": "3xTF32 (fp32 accumulate)", "complex64": "3xTF32 (fp32 accumulate)"}
@@ -456,6 +457,9 @@ def main():
     ap.add_argument("--bcast", default=None, choices=[None, "p2p", "broadcast", "scatter_allgather"])
     ap.add_argument("--overlap", default=None, choices=[None, "fused", "single", "panels"])
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
+    ap.add_argument("--scatter", default=DEFAULT_SCATTER, choices=["push", "pull", "multicast"],
+                    help="how B leaves the owner in the fused multi-GPU kernel")
+    ap.add_argument("--owner-less", type=int, default=0, help="256-row blocks the owner of B hands to the other ranks")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident loop only (no end-to-end leg, no extras): the command profiled under ncu")
@@ -519,7 +523,8 @@ def main():
 
     # ------------------------------------------------------------ device-resident measurement
     panels = args.panels if args.panels == "ramp" else int(args.panels)
-    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast, overlap=args.overlap)
+    sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast,
+                     overlap=args.overlap, scatter=args.scatter, owner_blocks_less=args.owner_less)
     if sg.nrows:
         sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
     if sg.is_owner:
@@ -671,7 +676,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": ARITH[dtype], "data": "synthetic (seeded, generated on the device)",
         "config": {"workload": args.workload, "description": DESCR[args.workload], "M": M, "N": N, "K": K,
-                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, overlap={sg.overlap}, gather={sg.gather}" if world > 1 else ""),
+                   "parallelism": f"rows of A over {world} GPU(s)" + (f", B in {len(sg.panels)} panels via {sg.bcast}, overlap={sg.overlap}, scatter={getattr(sg, '_scatter', None)}, gather={sg.gather}" if world > 1 else ""),
                    "l2": "inputs (A+B+D = %.1f GiB) exceed the 126 MB L2; no flush between steps" % ((M * K + K * N + M * N) * esz / 2 ** 30),
                    "sample": "the whole problem, every step"},
         "pct_of_peak": {"value": 100 * value / (world * peak), "denominator_tflops": world * peak,

@@ -52,16 +52,29 @@ ROW_ALIGN = 256
 COL_ALIGN = 256
 
 
-def row_ranges(M, world, align=ROW_ALIGN):
+def row_ranges(M, world, align=ROW_ALIGN, lighter=None):
     """[(first_row, rows)] per rank: equal blocks of whole `align`-row tiles, the remainder on the
-    last ranks that still get rows; ranks beyond the data get (M, 0)."""
+    last ranks that still get rows; ranks beyond the data get (M, 0).
+
+    lighter = (rank, k): that rank gets k blocks fewer and the others share them (the owner of B spends part of
+    its SMs' time sending B; with a smaller share it finishes together with the others).  Ignored when the
+    matrix has too few blocks for it."""
     blocks = (M + align - 1) // align
     per = (blocks + world - 1) // world
-    out = []
+    counts = [max(0, min(per, blocks - r * per)) for r in range(world)]
+    if lighter is not None and world > 1:
+        rank, k = lighter
+        if 0 < k < counts[rank] and all(c > 0 for c in counts):
+            counts[rank] -= k
+            others = [r for r in range(world) if r != rank]
+            for i in range(k):
+                counts[others[-1 - (i % len(others))]] += 1
+    out, start = [], 0
     for r in range(world):
-        start = min(M, r * per * align)
-        stop = min(M, (r + 1) * per * align)
-        out.append((start, stop - start))
+        first = min(M, start * align)
+        stop = min(M, (start + counts[r]) * align)
+        out.append((first, stop - first))
+        start += counts[r]
     return out
 
 
@@ -203,7 +216,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push"):
+                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push", owner_blocks_less=0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -220,7 +233,7 @@ class ShardedGemm:
         # until the GEMM ends and the pipeline becomes broadcast-bound.
         self._reserve_arg = reserve_sms
         self.gather = gather or ("peer" if self.on_gpu and self.world > 1 else "collective")
-        self.rows = row_ranges(M, self.world)
+        self.rows = row_ranges(M, self.world, lighter=(owner, owner_blocks_less) if owner_blocks_less else None)
         self.row0, self.nrows = self.rows[self.rank]
         self.panels = panel_plan(N, panels if self.world > 1 else 1)
         self.is_owner = self.rank == owner

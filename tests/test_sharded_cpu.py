@@ -28,6 +28,13 @@ def test_row_ranges_cover_and_align():
                     pos += n
     assert row_ranges(65536, 8) == [(i * 8192, 8192) for i in range(8)]
     assert row_ranges(300, 4) == [(0, 256), (256, 44), (300, 0), (300, 0)]
+    # a lighter share for one rank: its blocks go to the others, everything still covered in order
+    rr = row_ranges(65536, 8, lighter=(0, 2))
+    assert rr[0] == (0, 30 * 256) and sum(n for _, n in rr) == 65536 and sorted(n // 256 for _, n in rr) == [30, 32, 32, 32, 32, 32, 33, 33]
+    assert all(a[0] + a[1] == b[0] for a, b in zip(rr, rr[1:]))
+    rr = row_ranges(65536, 8, lighter=(3, 1))
+    assert rr[3][1] == 31 * 256 and rr[7][1] == 33 * 256 and all(a[0] + a[1] == b[0] for a, b in zip(rr, rr[1:]))
+    assert row_ranges(300, 4, lighter=(0, 1)) == row_ranges(300, 4)          # too few blocks: unchanged
 
 
 def test_panel_plan():
