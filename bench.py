@@ -240,11 +240,13 @@ def variant_name(v):
     """decxb200_last_kernel_variant() -> the kernel's template name."""
     if not v:
         return None
-    narrow, v = divmod(v, 5000)
+    conv, v = divmod(v, 20000)
+    bn = 128 if v >= 6000 else (64 if v >= 5000 else 0)
+    v -= {128: 6000, 64: 5000, 0: 0}[bn]
     fetch, v = divmod(v, 1000)
     kind, rest = divmod(v, 100)
     ctas, nacc = divmod(rest, 10)
-    return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}{',64' if narrow else ''}>"
+    return f"gemm_tcgen05_kernel<{kind},{ctas},{nacc},{2 if fetch else 0}{',%d' % bn if bn else ''}>" + (" (implicit conv)" if conv else "")
 
 
 def hbm_peak():
@@ -461,6 +463,8 @@ def main():
                     help="how B leaves the owner in the fused multi-GPU kernel")
     ap.add_argument("--owner-less", type=int, default=0, help="256-row blocks the owner of B hands to the other ranks")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
+    ap.add_argument("--aux", default=None, choices=sorted(AUX),
+                    help="time ONE of the bandwidth-bound / auxiliary kernels and print its record (the command profiled under ncu)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident loop only (no end-to-end leg, no extras): the command profiled under ncu")
     args = ap.parse_args()
@@ -470,6 +474,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.aux is not None:
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps(time_aux(torch, args.aux, torch.device("cuda", 0), iters=max(args.steps, 1), warmup=max(args.warmup, 1))))
+        return
 
     # Libraries (NCCL's version banner, torchrun notices) may write to stdout; the contract is ONE JSON line
     # there.  Everything else goes to stderr: fd 1 is pointed at stderr and the line is written to the saved fd.

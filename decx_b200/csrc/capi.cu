@@ -46,7 +46,7 @@ constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
     unsigned ticket_base = 0;   // next starting value of the kernels' tile-barrier ticket counter
     int sm_count = 0;
-    bool attr_set[2][2][2][4] = {};
+    bool attr_set[2][2][2][6] = {};
 };
 DeviceInfo g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
@@ -165,10 +165,10 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
             cudaError_t e = cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess) return int(e);
         }
-        if (!di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV != 256 ? 2 : 0)]) {
+        if (!di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV == 64 ? 2 : 0) + (BNV == 128 ? 4 : 0)]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
             if (e != cudaSuccess) return int(e);
-            di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV != 256 ? 2 : 0)] = true;
+            di.attr_set[KIND][CTAS - 1][NACC - 1][(FETCH ? 1 : 0) + (BNV == 64 ? 2 : 0) + (BNV == 128 ? 4 : 0)] = true;
         }
     }
     p.tiles_m = uint32_t((uint64_t(p.M) + Cfg::BM * CTAS - 1) / (Cfg::BM * CTAS));
@@ -234,7 +234,7 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, a1, b0, b1, dmap, cmap, p, f);
     if (e != cudaSuccess) return int(e);
     ++t_launches;
-    t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0) + (BNV != 256 ? 5000 : 0);
+    t_variant = KIND * 100 + CTAS * 10 + NACC + (FETCH ? 1000 : 0) + (BNV == 64 ? 5000 : 0) + (BNV == 128 ? 6000 : 0);
     return 0;
 }
 
@@ -673,8 +673,11 @@ int dxb_host::conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsig
     p.conv_tiles_x = tiles_x;
     p.conv_kbi = kbi;
     p.b_chunked_map = 1;
-    const bool narrow = c.n <= 128;
-    const uint32_t chunks = narrow ? GemmCfg<1, 1, 1, 0, 64>::B_CHUNKS : GemmCfg<1, 1>::B_CHUNKS;
+    // accumulator width: the narrowest of 64 / 128 / 256 columns that takes all kernels in one tile column (a wider
+    // tile re-reads the source tile less often, an over-wide one multiplies zeros)
+    const int bn = c.n <= 64 ? 64 : (c.n <= 128 ? 128 : 256);
+    const uint32_t chunks = bn == 64 ? GemmCfg<1, 1, 1, 0, 64>::B_CHUNKS
+                                     : (bn == 128 ? GemmCfg<1, 1, 1, 0, 128>::B_CHUNKS : GemmCfg<1, 1>::B_CHUNKS);
     using C1 = GemmCfg<1, 1>;
     CUtensorMap b0, b1;
     int rc;
@@ -684,8 +687,9 @@ int dxb_host::conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsig
     if ((rc = make_map_b_chunked(&b1, false, c.b_lo, p.K, c.n, c.ldbw, C1::CHUNK_N, C1::BK, chunks,
                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
-    rc = narrow ? launch_gemm<1, 1, 1, 0, 64>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
-                : launch_gemm<1, 1>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    rc = bn == 64    ? launch_gemm<1, 1, 1, 0, 64>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
+         : bn == 128 ? launch_gemm<1, 1, 1, 0, 128>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
+                     : launch_gemm<1, 1>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
     if (rc == 0) t_variant += 20000;
     return rc;
 }

@@ -177,13 +177,14 @@ __device__ unsigned g_wave_ticket;
 
 template <int KIND, int CTAS, int NACC = 1, int FETCH = 0, int BNV = 256>
 struct GemmCfg {
-    static_assert(BNV == 256 || (BNV == 64 && KIND == 1 && CTAS == 1), "narrow accumulators: 3xTF32 single-CTA tiles only");
+    static_assert(BNV == 256 || ((BNV == 64 || BNV == 128) && KIND == 1 && CTAS == 1),
+                  "narrow accumulators: 3xTF32 single-CTA tiles only");
     static_assert(NACC == 1 || (NACC == 2 && KIND == 0 && CTAS == 2), "two accumulators per tile: fp16 CTA pairs only");
     static_assert(FETCH == 0 || (KIND == 0 && CTAS == 2), "courier warps: fp16 CTA pairs only");
     static constexpr int ELEM = (KIND == 0) ? 2 : 4;
     static constexpr int NPL = (KIND == 0) ? 1 : 2;       // operand planes (hi, lo)
     static constexpr int BM = 128;                        // rows per CTA
-    static constexpr int BN = BNV;                        // UMMA N = columns of one accumulator (64: small problems)
+    static constexpr int BN = BNV;                        // UMMA N = columns of one accumulator (64, 128: small problems, few kernels)
     static constexpr int BN_TILE = BN * NACC;             // columns of one tile (NACC accumulators share each A tile)
     static constexpr int BN_LOAD = BN_TILE / CTAS;        // columns of B this CTA loads per stage
     static constexpr int BK = 128 / ELEM;                 // one 128-byte swizzle row of K

@@ -361,7 +361,8 @@ DECXB200_API int decxb200_last_launch_count(void);
 
 /* Which GEMM kernel the last call of this thread launched: 100*KIND + 10*CTAS + NACC
  * (KIND 0 = fp16, 1 = 3xTF32; CTAS = CTAs per tile; NACC = 256-column accumulators per tile), + 1000 when the kernel
- * carried courier warps, + 5000 for the 128 x 64 tile small 3xTF32 problems get;
+ * carried courier warps, + 5000 / + 6000 for the 128 x 64 / 128 x 128 tiles of small 3xTF32 problems and of
+ * convolutions with few kernels, + 20000 when the kernel ran as an implicit-GEMM convolution;
  * e.g. 22 = fp16 256x512 pair tile, 121 = 3xTF32 256x256 pair tile, 5111 = 3xTF32 128x64 tile. */
 DECXB200_API int decxb200_last_kernel_variant(void);
 
