@@ -170,7 +170,8 @@ int decxb200_cast2d(int kind, void* stream_, uint32_t rows, uint32_t cols, const
     if (src == nullptr || dst == nullptr || rows == 0 || cols == 0 || lds < cols || ldd < cols) return DECXB200_EINVAL;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
     const uint64_t work = uint64_t(rows) * ((cols + 1) / 2);
-    const unsigned blocks = unsigned(work / 256 + 1 > 148ull * 64 ? 148ull * 64 : work / 256 + 1);
+    // a thread converts four groups per round: a quarter of the blocks, capped at 32 per SM
+    const unsigned blocks = unsigned(work / 1024 + 1 > 148ull * 32 ? 148ull * 32 : work / 1024 + 1);
 #define DXB_CAST(KIND)                                                                                              \
     {                                                                                                               \
         using S = CastTypes<KIND>::S;                                                                               \

@@ -6,6 +6,7 @@
 //       the fp32<->fp16 pair is new here -- it is what produces the operands of the fp16 GEMM on the device).
 // Each reads its input once and writes its output once.
 #pragma once
+#include <type_traits>
 #include <cuda_fp16.h>
 #include <cstdint>
 
@@ -184,21 +185,47 @@ cast2d_kernel(const typename CastTypes<KIND>::S* __restrict__ src, uint64_t lds,
     constexpr int G = 16 / WIDE;                                  // 4 (4-byte wide side) or 2 (8-byte wide side)
     const uint32_t groups = (cols + G - 1) / G;
     const uint64_t total = uint64_t(rows) * groups;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
-        const uint32_t r = uint32_t(i / groups), c = uint32_t(i % groups) * G;
-        const S* s = src + uint64_t(r) * lds + c;
-        D* d = dst + uint64_t(r) * ldd + c;
-        if (vec_ok && c + G <= cols) {
-            S in[G];
-            D out[G];
-            if constexpr (G * sizeof(S) == 16) *reinterpret_cast<uint4*>(in) = __ldcs(reinterpret_cast<const uint4*>(s));
-            else *reinterpret_cast<uint2*>(in) = __ldcs(reinterpret_cast<const uint2*>(s));
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    constexpr int U = 4;                     // groups per thread and round: all loads are issued before the first store
+    using LoadT = typename std::conditional<G * sizeof(S) == 16, uint4, uint2>::type;
+    using StoreT = typename std::conditional<G * sizeof(D) == 16, uint4, uint2>::type;
+    for (uint64_t i0 = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i0 < total; i0 += U * stride) {
+        if (vec_ok && (cols % G) == 0 && i0 + (U - 1) * stride < total) {
+            LoadT in[U];
+            D* d[U];
 #pragma unroll
-            for (int e = 0; e < G; ++e) out[e] = cast1<KIND>(in[e]);
-            if constexpr (G * sizeof(D) == 16) __stcs(reinterpret_cast<uint4*>(d), *reinterpret_cast<const uint4*>(out));
-            else __stcs(reinterpret_cast<uint2*>(d), *reinterpret_cast<const uint2*>(out));
-        } else {
-            for (int e = 0; e < G && c + e < cols; ++e) d[e] = cast1<KIND>(s[e]);
+            for (int u = 0; u < U; ++u) {
+                const uint64_t i = i0 + u * stride;
+                const uint32_t r = uint32_t(i / groups), c = uint32_t(i % groups) * G;
+                in[u] = __ldcs(reinterpret_cast<const LoadT*>(src + uint64_t(r) * lds + c));
+                d[u] = dst + uint64_t(r) * ldd + c;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const S* sv = reinterpret_cast<const S*>(&in[u]);
+                D out[G];
+#pragma unroll
+                for (int e = 0; e < G; ++e) out[e] = cast1<KIND>(sv[e]);
+                __stcs(reinterpret_cast<StoreT*>(d[u]), *reinterpret_cast<const StoreT*>(out));
+            }
+            continue;
+        }
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + u * stride;
+            if (i >= total) break;
+            const uint32_t r = uint32_t(i / groups), c = uint32_t(i % groups) * G;
+            const S* s = src + uint64_t(r) * lds + c;
+            D* d = dst + uint64_t(r) * ldd + c;
+            if (vec_ok && c + G <= cols) {
+                S in[G];
+                D out[G];
+                *reinterpret_cast<LoadT*>(in) = __ldcs(reinterpret_cast<const LoadT*>(s));
+#pragma unroll
+                for (int e = 0; e < G; ++e) out[e] = cast1<KIND>(in[e]);
+                __stcs(reinterpret_cast<StoreT*>(d), *reinterpret_cast<const StoreT*>(out));
+            } else {
+                for (int e = 0; e < G && c + e < cols; ++e) d[e] = cast1<KIND>(s[e]);
+            }
         }
     }
 }
