@@ -818,7 +818,7 @@ int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
             if (rc == 0)
                 rc = run_tf32(hp->comp, dev, cplx, rows, N, K, a_hi, a_lo, ar.ldaw,
                               reinterpret_cast<float*>(at(ar.b_hi)), reinterpret_cast<float*>(at(ar.b_lo)), ar.ldbw,
-                              c_dev, ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, sc, status, cta_group, 0);
+                              c_dev, ar.ldcd_d, at(ar.d_dev[b]), ar.ldcd_d, sc, status, cta_group, 0, true);
         }
         if (rc != 0) { cudaDeviceSynchronize(); return rc; }
         DXB_CUDA(cudaEventRecord(hp->ev_comp[b], hp->comp));

@@ -29,3 +29,16 @@ def test_other_ranks_of_the_reference_arm_stay_silent():
                         "--workload", "cfg1", "--steps", "1", "--warmup", "0"], capture_output=True, text=True,
                        timeout=600, cwd=ROOT, env=env)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_kernel_variant_names():
+    """decxb200_last_kernel_variant() codes -> template names, as bench.py prints them in `roofline.kernel`."""
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.variant_name(0) is None
+    assert bench.variant_name(22) == "gemm_tcgen05_kernel<0,2,2,0>"
+    assert bench.variant_name(1022) == "gemm_tcgen05_kernel<0,2,2,2>"
+    assert bench.variant_name(121) == "gemm_tcgen05_kernel<1,2,1,0>"
+    assert bench.variant_name(5111) == "gemm_tcgen05_kernel<1,1,1,0,64>"
+    assert bench.variant_name(26111) == "gemm_tcgen05_kernel<1,1,1,0,128> (implicit conv)"
+    assert bench.variant_name(20111) == "gemm_tcgen05_kernel<1,1,1,0> (implicit conv)"
