@@ -461,6 +461,8 @@ def main():
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--scatter", default=DEFAULT_SCATTER, choices=["push", "pull", "multicast"],
                     help="how B leaves the owner in the fused multi-GPU kernel")
+    ap.add_argument("--direct-d", action="store_true",
+                    help="multi-GPU: epilogues store D straight into the owner's memory (no forwarding by the couriers)")
     ap.add_argument("--owner-less", type=int, default=0, help="256-row blocks the owner of B hands to the other ranks")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--aux", default=None, choices=sorted(AUX),
@@ -533,7 +535,8 @@ def main():
     # ------------------------------------------------------------ device-resident measurement
     panels = args.panels if args.panels == "ramp" else int(args.panels)
     sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast,
-                     overlap=args.overlap, scatter=args.scatter, owner_blocks_less=args.owner_less)
+                     overlap=args.overlap, scatter=args.scatter, owner_blocks_less=args.owner_less,
+                     forward_d=not args.direct_d)
     if sg.nrows:
         sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
     if sg.is_owner:

@@ -71,6 +71,10 @@ def _load():
     lib.decxb200_gemm_fp16_fetch.restype = ci
     lib.decxb200_gemm_fp16_fetch.argtypes = [vp, u32, u32, u32, vp, u64, vp, u64, vp, u64, vp, u32, ctypes.POINTER(u32),
                                              vp, vp, ctypes.c_uint, ctypes.POINTER(FetchJob), u32, vp, sz, ci, ci]
+    lib.decxb200_gemm_fp16_fetch_staged.restype = ci
+    lib.decxb200_gemm_fp16_fetch_staged.argtypes = lib.decxb200_gemm_fp16_fetch.argtypes + [vp, sz]
+    lib.decxb200_fetch_d_stage_bytes.restype = sz
+    lib.decxb200_fetch_d_stage_bytes.argtypes = []
     lib.decxb200_gemv_workspace_bytes.restype = sz
     lib.decxb200_gemv_workspace_bytes.argtypes = [ci, ci, ci, u32, u32]
     lib.decxb200_gemv.restype = ci
@@ -124,7 +128,7 @@ EXPORTS = [
     "decxb200_gemm_host_multi",
     "decxb200_gemm_fp32_noalloc", "decxb200_gemv_workspace_bytes", "decxb200_gemv", "decxb200_transpose",
     "decxb200_cast2d", "decxb200_conv2d_fp32_out_dims", "decxb200_conv2d_fp32_workspace_bytes", "decxb200_conv2d_fp32",
-    "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_copy2d_async", "decxb200_write_flag_async",
+    "decxb200_gemm_fp16_panels", "decxb200_fetch_scratch_bytes", "decxb200_gemm_fp16_fetch", "decxb200_gemm_fp16_fetch_staged", "decxb200_fetch_d_stage_bytes", "decxb200_copy2d_async", "decxb200_write_flag_async",
     "decxb200_ipc_alloc", "decxb200_ipc_free", "decxb200_ipc_export", "decxb200_ipc_open", "decxb200_ipc_close",
     "decxb200_last_launch_count", "decxb200_last_kernel_variant", "decxb200_tensor_map_cache_stats", "decxb200_debug_stats", "decxb200_strerror", "decxb200_version",
 ]

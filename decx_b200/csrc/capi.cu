@@ -210,6 +210,18 @@ int launch_gemm(cudaStream_t stream, int dev, const CUtensorMap& a0, const CUten
         di.ticket_base += unsigned(tiles);       // every launch adds exactly one ticket per tile
     }
 
+    if constexpr (FETCH > 0) {
+        // D forwarding: a ring of two 128 x 512 fp16 tiles per CTA in local memory, mapped like D (64 x 32 boxes)
+        const uint64_t ring_rows = uint64_t(workers) * CTAS * 2 * Cfg::BM;
+        if (f.fwd_stage != nullptr && NACC == 2 && p.d_tma && f.fwd_stage_bytes >= ring_rows * 1024 &&
+            aligned16(f.fwd_stage) && (p.N % 8) == 0 &&
+            make_map(&cmap, true, f.fwd_stage, ring_rows, 512, 512, 64, 32) == 0) {
+            p.c_tma = 0;
+        } else {
+            f.fwd_stage = nullptr;
+        }
+    }
+
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(workers * CTAS, 1, 1);
@@ -936,11 +948,23 @@ size_t decxb200_fetch_scratch_bytes(uint32_t n_jobs) {
     return FETCH_TABLE_OFF + size_t(round_up(uint64_t(n_jobs) * sizeof(FetchJob), 256)) + size_t(round_up(uint64_t(n_jobs) * 4, 256));
 }
 
+size_t decxb200_fetch_d_stage_bytes(void) { return size_t(256) * 2 * 128 * 1024; }     // up to 256 CTAs
+
 int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, void* B,
                              uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
                              const uint32_t* panel_col_end, unsigned* ready_flags, unsigned* pub_flags, unsigned epoch,
                              const decxb200_fetch_job* jobs, uint32_t n_jobs, void* scratch, size_t scratch_bytes,
                              int max_ctas, int tile) {
+    return decxb200_gemm_fp16_fetch_staged(stream_, M, N, K, A, lda, B, ldb, D, ldd, status, n_panels, panel_col_end,
+                                           ready_flags, pub_flags, epoch, jobs, n_jobs, scratch, scratch_bytes, max_ctas,
+                                           tile, nullptr, 0);
+}
+
+int decxb200_gemm_fp16_fetch_staged(void* stream_, uint32_t M, uint32_t N, uint32_t K, const void* A, uint64_t lda, void* B,
+                                    uint64_t ldb, void* D, uint64_t ldd, unsigned* status, uint32_t n_panels,
+                                    const uint32_t* panel_col_end, unsigned* ready_flags, unsigned* pub_flags,
+                                    unsigned epoch, const decxb200_fetch_job* jobs, uint32_t n_jobs, void* scratch,
+                                    size_t scratch_bytes, int max_ctas, int tile, void* d_stage, size_t d_stage_bytes) {
     t_launches = 0;
     int dev = 0, cta_group = (tile == DECXB200_TILE_256x512) ? tile : 2;
     int rc = check_common(DECXB200_FP16, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, cta_group, dev);
@@ -1025,6 +1049,8 @@ int decxb200_gemm_fp16_fetch(void* stream_, uint32_t M, uint32_t N, uint32_t K, 
     f.ready_flags = ready_flags;
     f.pub_flags = pub_flags;
     f.epoch = epoch;
+    f.fwd_stage = static_cast<uint8_t*>(d_stage);
+    f.fwd_stage_bytes = d_stage_bytes;
     return run_f16(stream, dev, M, N, K, A, lda, B, ldb, nullptr, 0, D, ldd, Scalars(), status, cta_group, max_ctas,
                    any_pull ? &g : nullptr, &f);
 }

@@ -163,6 +163,15 @@ struct FetchParams {
     unsigned epoch;
     uint32_t need[MAX_PANELS];       // batches per panel
     uint32_t pub_need[MAX_PANELS];   // publishing batches per panel (0: nothing to publish)
+    // D forwarding (256 x 512 tiles only; nullptr: the epilogue stores D directly).  When D lives in another GPU's
+    // memory, every CTA of every GPU finishes its tile at about the same time and the TMA stores of all of them hit
+    // one NVLink port as a burst; the accumulators are released only when the last box has left shared memory, so
+    // the burst delays the next tile's MMAs (measured: 6 % on the sender, 9 % on the receiver whose own epilogue
+    // collides with it).  With a stage the epilogue stores its part of the tile into a ring of two tiles per CTA in
+    // LOCAL memory (it stays in L2), and the courier warps copy it to D with plain 16-byte stores while the next
+    // tile is being multiplied.  Layout: CTA b, ring slot s, row r: fwd_stage + ((b * 2 + s) * 128 + r) * 1024 bytes.
+    uint8_t* fwd_stage;
+    uint64_t fwd_stage_bytes;        // host side only: size of the ring area
 };
 
 // Ticket counter of the soft tile barrier.  All CTAs of a launch are resident at once (one per SM), and
@@ -204,7 +213,8 @@ struct GemmCfg {
     static constexpr int ACC_ARRIVALS = (EPI_WARPS / NACC) * CTAS;   // epilogue warps (of the pair) per accumulator
     static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * FETCH;
     static constexpr int STAGING = EPI_WARPS * 4096;      // per epilogue warp: 32 rows x 128 bytes of output
-    static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int MAILBOX = (FETCH > 0) ? 64 : 0;  // D forwarding: parts published / forwarded per epilogue warp
+    static constexpr int SMEM_BYTES = STAGES * STAGE + STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/ + MAILBOX;
     static_assert(16 * STAGES + 32 + 8 + 16 + 8 * EPI_WARPS <= 256, "barrier area");
     static constexpr uint32_t IDESC = umma_idesc(KIND == 0 ? 0u : 2u, false, true, BM * CTAS, BN);
 };
@@ -529,6 +539,34 @@ struct Courier {
     }
 };
 
+// D forwarding: copies the part of this CTA's k-th tile that epilogue warp w (= warp 2 + w of the CTA: rows
+// 32 * ((w + 2) & 3), the tensor-memory lanes that warp may read; accumulator w >> 2
+// = tile columns [128a, +128) and [256 + 128a, +128)) staged in the CTA's ring to D, clipped at M and N.  One warp:
+// lanes 0..15 carry the first 256-byte span of a row, lanes 16..31 the second.
+__device__ __forceinline__ void forward_part(const FetchParams& f, const GemmParams& p, uint32_t lane, uint32_t w, uint32_t k,
+                                             uint32_t worker, uint32_t n_workers, uint32_t cta_rank) {
+    uint32_t tm, tn;
+    tile_coords(worker + k * n_workers, p, tm, tn);
+    const uint32_t q = (w + 2u) & 3u, a = w >> 2;
+    const uint32_t row0 = (tm * 2 + cta_rank) * 128 + q * 32;
+    const uint32_t colt = (lane < 16 ? 0u : 256u) + a * 128 + (lane & 15u) * 8;       // column within the tile
+    const uint32_t col = tn * 512 + colt;
+    const uint32_t rows = (row0 < p.M && col < p.N) ? min(32u, p.M - row0) : 0u;
+    const uint8_t* src = f.fwd_stage + (uint64_t(blockIdx.x * 2 + (k & 1u)) * 128 + q * 32) * 1024 + colt * 2;
+    uint8_t* dst = static_cast<uint8_t*>(p.D) + (uint64_t(row0) * p.ldd + col) * 2;
+    const uint64_t dpitch = p.ldd * 2;
+#pragma unroll 1
+    for (uint32_t r0 = 0; r0 < rows; r0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+            if (r0 + u < rows) v[u] = ld_volatile_v4(src + uint64_t(r0 + u) * 1024);
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+            if (r0 + u < rows) *reinterpret_cast<uint4*>(dst + uint64_t(r0 + u) * dpitch) = v[u];
+    }
+}
+
 template <int KIND, int CTAS, int NACC, int FETCH, int BNV = 256>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, NACC, FETCH, BNV>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
@@ -551,6 +589,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const uint32_t cbar_base = acce_bar + 24;                // EPI_WARPS x 8 B: arrival of a box of C in a warp's staging tile
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    // D forwarding mailbox: [w] parts published by epilogue warp w, [8 + w] parts of that warp copied to D
+    volatile uint32_t* mbox = reinterpret_cast<volatile uint32_t*>(smem_raw + (bar_base + 256 - smem_u32(smem_raw)));
+    bool fwd = false;
+    if constexpr (FETCH > 0 && NACC == 2) fwd = f.fwd_stage != nullptr;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -565,6 +607,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const uint32_t chunk_kb = Cfg::PROMOTE ? uint32_t(Cfg::CHUNK_KB) : n_kb;
     const uint32_t n_chunks = (n_kb + chunk_kb - 1) / chunk_kb;
 
+    if constexpr (FETCH > 0) {
+        if (threadIdx.x >= 32 && threadIdx.x < 48) mbox[threadIdx.x - 32] = 0u;
+    }
     if (threadIdx.x == 0) {
         if (p.stats != nullptr && blockIdx.x == 0) p.stats[16] = global_timer_ns();
         for (int s = 0; s < STAGES; ++s) {
@@ -802,7 +847,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     } else if (FETCH > 0 && warp >= 2u + Cfg::EPI_WARPS) {
         // ------------------------------------------------------------------ couriers (B from the other GPUs)
         Courier c;
-        while (!c.done) c.step(f, p, lane, true);
+        if (!fwd) {
+            while (!c.done) c.step(f, p, lane, true);
+        } else {
+            // two couriers per CTA: each also forwards the finished parts of four epilogue warps to D, between
+            // batches of B (a part is 32 KB once per tile: B is hardly delayed, and the ring gives D a tile's time)
+            const uint32_t cw = warp - (2u + Cfg::EPI_WARPS);
+            const uint32_t my_tiles = n_tiles > worker ? (n_tiles - worker - 1) / n_workers + 1 : 0u;
+            uint32_t sent[4] = {0u, 0u, 0u, 0u};
+            uint64_t idle_since = global_timer_ns();
+            for (;;) {
+                bool progressed = false, all_sent = true;
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    const uint32_t w = cw + 2 * j;
+                    if (sent[j] < my_tiles) {
+                        uint32_t seq = 0;
+                        if (lane == 0) seq = mbox[w];
+                        seq = __shfl_sync(0xffffffffu, seq, 0);
+                        if (seq > sent[j]) {
+                            __threadfence();                 // the part's bytes, written before the count
+                            forward_part(f, p, lane, w, sent[j], worker, n_workers, cta_rank);
+                            ++sent[j];
+                            __syncwarp();
+                            if (lane == 0) mbox[8 + w] = sent[j];     // the ring slot may be overwritten
+                            progressed = true;
+                        }
+                        if (sent[j] < my_tiles) all_sent = false;
+                    }
+                }
+                if (!c.done) {
+                    c.step(f, p, lane, false);               // its own waits are bounded
+                    idle_since = global_timer_ns();
+                    continue;
+                }
+                if (all_sent) break;
+                if (progressed) {
+                    idle_since = global_timer_ns();
+                } else {
+                    if (global_timer_ns() - idle_since > limit) {       // the epilogue gave up: nothing more will come
+                        if (lane == 0) report(p, KS_TIMEOUT_FETCH);
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+            }
+        }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..)
         const uint32_t quarter = warp & 3u;                  // TMEM lanes [32*quarter, +32) belong to this warp
@@ -924,6 +1014,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 }
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + a * Cfg::BN + ((quarter * 32u) << 16);
+                if (fwd && it >= 2) {
+                    // D forwarding: this part goes into ring slot it & 1; the part staged there two tiles ago must
+                    // have been copied to D (it had a whole tile's time: normally no wait at all)
+                    uint32_t gone = 1;
+                    if (lane == 0) {
+                        const uint64_t t0 = global_timer_ns();
+                        while (mbox[8 + (warp - 2u)] + 2u <= it) {
+                            if (global_timer_ns() - t0 > limit) { gone = 0; break; }
+                            __nanosleep(100);
+                        }
+                    }
+                    gone = __shfl_sync(0xffffffffu, gone, 0);
+                    if (!gone) {
+                        if (lane == 0) report(p, KS_TIMEOUT_EPILOGUE);
+                        ok = false;
+                        break;
+                    }
+                }
 #pragma unroll 1
                 for (uint32_t c = 0; c < Cfg::EPI_COLS / 32; ++c) {
                     // accumulator column 32c -> matrix column.  NACC 2: columns 0..127 of accumulator h come from
@@ -957,7 +1065,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                             const uint32_t warp_row0 = (tm * CTAS + cta_rank) * Cfg::BM + quarter * 32;
                             fence_proxy_async_smem();
                             __syncwarp();
-                            if (lane == 0 && warp_row0 < p.M) {
+                            if (fwd) {
+                                // into this CTA's ring in local memory (tmC maps it: 512 columns, 128 rows per slot)
+                                if (lane == 0) {
+                                    tma_store_2d(&tmC, stage_warp, int32_t(col0 - half * 32 - tn * Cfg::BN_TILE),
+                                                 int32_t((blockIdx.x * 2 + (it & 1u)) * Cfg::BM + quarter * 32));
+                                    bulk_commit_group();
+                                }
+                            } else if (lane == 0 && warp_row0 < p.M) {
                                 tma_store_2d(&tmD, stage_warp, int32_t(col0 - half * 32), int32_t(warp_row0));
                                 bulk_commit_group();
                             }
@@ -971,6 +1086,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 if (lane == 0) {
                     if constexpr (CTAS == 2) mbar_arrive_cluster(acce_target + 8 * a);
                     else mbar_arrive(acce_bar + 8 * a);
+                }
+                if (fwd) {
+                    // the part is complete in the ring: hand it to this CTA's couriers
+                    if (lane == 0) {
+                        bulk_wait_all();
+                        fence_proxy_async_all();
+                        __threadfence();
+                        mbox[warp - 2u] = it + 1u;
+                    }
+                    __syncwarp();
                 }
                 ++it;
             }

@@ -168,22 +168,25 @@ def gemm_fp16_panels(A, B, out, panel_col_end, flags, epoch, status=None, max_ct
 
 
 def gemm_fp16_fetch(A, B_replica, out_ptr, ldd, panel_col_end, ready_flags, pub_flags, epoch, jobs, scratch,
-                    status=None, max_ctas=0, tile=0):
+                    status=None, max_ctas=0, tile=0, d_stage=None):
     """One launch that brings B into ``B_replica`` (``jobs``: list of ``capi.FetchJob``) while it multiplies
-    (``decxb200_gemm_fp16_fetch``).  ``out_ptr`` is a raw device address (D may live in another GPU's memory).
-    Launches on torch's current stream."""
+    (``decxb200_gemm_fp16_fetch_staged``).  ``out_ptr`` is a raw device address (D may live in another GPU's
+    memory); ``d_stage``: local uint8 tensor of ``decxb200_fetch_d_stage_bytes()`` bytes through which the couriers
+    forward D, or None for direct stores.  Launches on torch's current stream."""
     M, K = A.shape
     N = B_replica.shape[1]
     ends = (ctypes.c_uint32 * len(panel_col_end))(*panel_col_end)
     arr = (capi.FetchJob * max(len(jobs), 1))(*jobs)
     with torch.cuda.device(A.device):
-        code = capi.lib.decxb200_gemm_fp16_fetch(
+        code = capi.lib.decxb200_gemm_fp16_fetch_staged(
             torch.cuda.current_stream().cuda_stream, M, N, K, A.data_ptr(), _ld(A), B_replica.data_ptr(), _ld(B_replica),
             out_ptr, ldd, status.data_ptr() if status is not None else None, len(panel_col_end), ends,
             ready_flags.data_ptr() if ready_flags is not None else None,
             pub_flags.data_ptr() if pub_flags is not None else None, epoch, arr, len(jobs),
             scratch.data_ptr() if scratch is not None else None,
-            scratch.numel() * scratch.element_size() if scratch is not None else 0, max_ctas, tile)
+            scratch.numel() * scratch.element_size() if scratch is not None else 0, max_ctas, tile,
+            d_stage.data_ptr() if d_stage is not None else None,
+            d_stage.numel() * d_stage.element_size() if d_stage is not None else 0)
     capi.check(code)
 
 

@@ -216,7 +216,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push", owner_blocks_less=0):
+                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push", owner_blocks_less=0, forward_d=True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -227,6 +227,7 @@ class ShardedGemm:
             raise RuntimeError("ShardedGemm computes on CUDA devices only (a host GEMM can only be injected by tests)")
         self.gemm_fn = gemm_fn
         self._scatter = scatter
+        self._forward_d = forward_d
         self.bcast = bcast or ("p2p" if self.on_gpu else "broadcast")
         # SMs left free for the communication kernels while a GEMM runs: the GEMM is persistent (one CTA per
         # SM for its whole duration), so without this NCCL's broadcast of the next panel cannot get an SM
@@ -388,6 +389,10 @@ class ShardedGemm:
         self._pulls = any(t[8] is None for t in tuples)
         need = int(capi.lib.decxb200_fetch_scratch_bytes(max(len(self._jobs), 1)))
         self._fetch_scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
+        # ranks whose D rows live in the owner's memory forward them through a local ring (see the C header)
+        self._d_stage = None
+        if self._forward_d and not self.is_owner and self.gather == "peer":
+            self._d_stage = torch.empty(int(capi.lib.decxb200_fetch_d_stage_bytes()), dtype=torch.uint8, device=self.device)
 
     def _fused_gemm(self, epoch, fetch=True):
         if self.nrows == 0:
@@ -400,7 +405,8 @@ class ShardedGemm:
             G.gemm_fp16_fetch(self.A, self.Bfull, self._d_ptr, self.N, ends, self.flags if gated else None,
                               self.pub_flags if (jobs and self._pulls) else None, epoch, jobs,
                               self._fetch_scratch if jobs else None,
-                              status=self.status, max_ctas=self._max_ctas, tile=self._tile)
+                              status=self.status, max_ctas=self._max_ctas, tile=self._tile,
+                              d_stage=self._d_stage if jobs else None)
         self.launches += self._capi.lib.decxb200_last_launch_count()
         self.kernel_variant = self._capi.lib.decxb200_last_kernel_variant()
 

@@ -345,6 +345,24 @@ DECXB200_API int decxb200_gemm_fp16_fetch(void* stream, uint32_t M, uint32_t N, 
                                           unsigned* ready_flags, unsigned* pub_flags, unsigned epoch,
                                           const decxb200_fetch_job* jobs, uint32_t n_jobs,
                                           void* scratch, size_t scratch_bytes, int max_ctas, int tile);
+/*
+ * The same call with a staging area for D (device memory of THIS GPU, 16-byte aligned, decxb200_fetch_d_stage_bytes()
+ * bytes; NULL = decxb200_gemm_fp16_fetch).  For a D that lives in another GPU's memory: the epilogue of a 256 x 512
+ * tile stores its boxes into a ring of two tiles per CTA in the staging area (local, L2-resident) and releases the
+ * accumulators at once; the courier warps copy each finished part to D with 16-byte stores while the next tile is
+ * being multiplied.  Without it all CTAs of all GPUs finish their tiles together and their TMA stores reach the
+ * owner's NVLink port as one burst that holds the accumulators (and so the next tile's MMAs) until it has drained.
+ * Used with the 256 x 512 tile only; other tiles store D directly.
+ */
+DECXB200_API size_t decxb200_fetch_d_stage_bytes(void);
+DECXB200_API int decxb200_gemm_fp16_fetch_staged(void* stream, uint32_t M, uint32_t N, uint32_t K,
+                                          const void* A, uint64_t lda, void* B, uint64_t ldb,
+                                          void* D, uint64_t ldd, unsigned* status,
+                                          uint32_t n_panels, const uint32_t* panel_col_end,
+                                          unsigned* ready_flags, unsigned* pub_flags, unsigned epoch,
+                                          const decxb200_fetch_job* jobs, uint32_t n_jobs,
+                                          void* scratch, size_t scratch_bytes, int max_ctas, int tile,
+                                                 void* d_stage, size_t d_stage_bytes);
 /* 2-D copy by the copy engines between any two device buffers this process can address (peer mappings
  * included): `rows` rows of `width_bytes`, rows dpitch / spitch bytes apart.  cudaMemcpy2DAsync. */
 DECXB200_API int decxb200_copy2d_async(void* stream, void* dst, size_t dpitch, const void* src, size_t spitch,

@@ -57,10 +57,15 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("staged", [False, True])
 @pytest.mark.parametrize("case", CASES)
-def test_fetch_from_local_stand_ins_gates_preset(G, dev, case):
+def test_fetch_from_local_stand_ins_gates_preset(G, dev, case, staged):
+    """staged: D leaves through the per-CTA ring and the couriers' 16-byte stores (what a rank does whose D rows live
+    in another GPU's memory) instead of the epilogue's own TMA stores; the guard rows and columns around D show
+    that the couriers clip at M and N."""
     from decx_b200 import capi
     M, N, K, ends, pieces, tile = case
+    d_stage = torch.empty(capi.lib.decxb200_fetch_d_stage_bytes(), dtype=torch.uint8, device=dev) if staged else None
     A, B, _ = make_inputs(np.float16, M, N, K, seed=K + N, dist="small")
     gA, gB = Guarded(torch, A, dev), Guarded(torch, B, dev)
     holders = [Guarded(torch, B, dev) for _ in pieces]                 # what the other "ranks" hold
@@ -74,7 +79,7 @@ def test_fetch_from_local_stand_ins_gates_preset(G, dev, case):
     jobs = _jobs(capi, src, [gates[i].data_ptr() for i in range(len(pieces))], K, ends, pieces, me=0)
     scratch = torch.empty(capi.lib.decxb200_fetch_scratch_bytes(len(jobs)), dtype=torch.uint8, device=dev)
     G.gemm_fp16_fetch(gA.view, gRep.view, gD.view.data_ptr(), gD.pitch, ends, ready, pub, 9, jobs, scratch,
-                      status=st, tile=tile)
+                      status=st, tile=tile, d_stage=d_stage)
     torch.cuda.synchronize()
     assert capi.lib.decxb200_last_kernel_variant() in (1021, 1022)
     assert int(st.item()) == 0
