@@ -787,19 +787,48 @@ int decxb200_gemm_host(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
     cudaError_t e;
 #define DXB_CUDA(call) do { e = (call); if (e != cudaSuccess) { cudaDeviceSynchronize(); return int(e); } } while (0)
 
-    // B: one copy, one split; every row block of A reuses it
-    DXB_CUDA(cudaMemcpy2DAsync(at(ar.b_dev), ar.ldb_d * es, B, ldb * es, uint64_t(N) * es, K, cudaMemcpyHostToDevice,
-                               hp->h2d));
-    DXB_CUDA(cudaEventRecord(hp->ev_b, hp->h2d));
-    DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_b, 0));
+    // Large fp16 B: nothing can be computed before B is on the device, and nothing downloaded before something is
+    // computed, so a 512 MiB B used to keep the download link idle for its whole upload.  Instead the first row block
+    // of A goes up first and B follows in eight column panels; each panel is multiplied with that block as soon as
+    // it has arrived and its piece of D goes down while the next panel comes up.
+    uint32_t first_rows = 0;
+    if (dtype == DECXB200_FP16 && !use_c && N >= 2048 && uint64_t(K) * N * es >= (64ull << 20)) {
+        first_rows = M < ar.rb ? M : ar.rb;
+        DXB_CUDA(cudaMemcpy2DAsync(at(ar.a_dev[0]), ar.lda_d * es, A, lda * es, uint64_t(K) * es, first_rows,
+                                   cudaMemcpyHostToDevice, hp->h2d));
+        const uint32_t pw = uint32_t(round_up((uint64_t(N) + 7) / 8, 64));
+        for (uint32_t c0 = 0; c0 < N; c0 += pw) {
+            const uint32_t w = N - c0 < pw ? N - c0 : pw;
+            uint8_t* b_panel = at(ar.b_dev) + uint64_t(c0) * es;
+            uint8_t* d_panel = at(ar.d_dev[0]) + uint64_t(c0) * es;
+            DXB_CUDA(cudaMemcpy2DAsync(b_panel, ar.ldb_d * es, static_cast<const uint8_t*>(B) + uint64_t(c0) * es, ldb * es,
+                                       uint64_t(w) * es, K, cudaMemcpyHostToDevice, hp->h2d));
+            DXB_CUDA(cudaEventRecord(hp->ev_b, hp->h2d));
+            DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_b, 0));
+            rc = run_f16(hp->comp, dev, first_rows, w, K, at(ar.a_dev[0]), ar.lda_d, b_panel, ar.ldb_d, nullptr, 0, d_panel,
+                         ar.ldcd_d, sc, status, cta_group, 0);
+            if (rc != 0) { cudaDeviceSynchronize(); return rc; }
+            DXB_CUDA(cudaEventRecord(hp->ev_comp[0], hp->comp));
+            DXB_CUDA(cudaStreamWaitEvent(hp->d2h, hp->ev_comp[0], 0));
+            DXB_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(D) + uint64_t(c0) * es, ldd * es, d_panel, ar.ldcd_d * es,
+                                       uint64_t(w) * es, first_rows, cudaMemcpyDeviceToHost, hp->d2h));
+        }
+        DXB_CUDA(cudaEventRecord(hp->ev_d2h[0], hp->d2h));
+    } else {
+        // B: one copy, one split; every row block of A reuses it
+        DXB_CUDA(cudaMemcpy2DAsync(at(ar.b_dev), ar.ldb_d * es, B, ldb * es, uint64_t(N) * es, K, cudaMemcpyHostToDevice,
+                                   hp->h2d));
+        DXB_CUDA(cudaEventRecord(hp->ev_b, hp->h2d));
+        DXB_CUDA(cudaStreamWaitEvent(hp->comp, hp->ev_b, 0));
+    }
     if (split) {
         rc = prep_b(hp->comp, cplx, at(ar.b_dev), ar.ldb_d, K, N, reinterpret_cast<float*>(at(ar.b_hi)),
                     reinterpret_cast<float*>(at(ar.b_lo)), ar.ldbw);
         if (rc != 0) { cudaDeviceSynchronize(); return rc; }
     }
     // row blocks: H2D of block i+1 and D2H of block i-1 overlap the GEMM of block i
-    uint32_t step = 0;
-    for (uint32_t r0 = 0; r0 < M; r0 += ar.rb, ++step) {
+    uint32_t step = first_rows ? 1 : 0;                     // buffers 0 are in use by the first block's panels
+    for (uint32_t r0 = first_rows; r0 < M; r0 += ar.rb, ++step) {
         const uint32_t rows = (M - r0 < ar.rb) ? M - r0 : ar.rb;
         const int b = int(step & 1u);
         const uint8_t* a_src = static_cast<const uint8_t*>(A) + uint64_t(r0) * lda * es;

@@ -235,6 +235,27 @@ def test_host_pointer_entry_point(G, dev, dt, pinned):
     assert torch.equal(D.cpu(), out[:, :N])
 
 
+def test_host_pointer_fp16_large_b_goes_up_in_column_panels(G, dev):
+    """fp16 with a B of 64 MiB and no C: the first row block is multiplied panel by panel of B while B is still
+    being uploaded (ragged M, N not a multiple of the panel width, pitched host matrices); same bits as the
+    device-pointer entry point, and the oracle agrees on sampled rows."""
+    M, N, K = 2300, 4104, 8192
+    A, B, _ = make_inputs(np.float16, M, N, K, seed=21, dist="small")
+    hp = lambda x: torch.from_numpy(np.pad(x, ((0, 0), (0, 8)))).pin_memory()[:, : x.shape[1]]
+    tA, tB = hp(A), hp(B)
+    st = G.new_status(dev)
+    out = torch.full((M, N + 8), float("nan"), dtype=torch.float16).pin_memory()
+    G.gemm_host(tA, tB, out=out[:, :N], status=st, device=dev)
+    assert int(st.item()) == 0
+    assert torch.isnan(out[:, N:]).all()
+    D = G.gemm(torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(D.cpu(), out[:, :N])
+    rows = [0, 1023, 1024, 2047, 2048, M - 1]
+    ref = ob.gemm(A[rows], B)
+    assert ob.metric(out[rows, :N].numpy(), ref, A[rows], B) <= TOL["float16"]
+
+
 def test_huge_finite_fp32_inputs_do_not_turn_into_nan(G, dev):
     """Values next to FLT_MAX: rounding them up to tf32 would overflow; the split keeps them finite."""
     rng = np.random.default_rng(12)
