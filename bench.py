@@ -463,7 +463,8 @@ def main():
                     help="how B leaves the owner in the fused multi-GPU kernel")
     ap.add_argument("--direct-d", action="store_true",
                     help="multi-GPU: epilogues store D straight into the owner's memory (no forwarding by the couriers)")
-    ap.add_argument("--owner-less", type=int, default=0, help="256-row blocks the owner of B hands to the other ranks")
+    ap.add_argument("--owner-less", type=int, default=None,
+                    help="256-row blocks the owner of B hands to the other ranks (default: 2 at 8 GPUs, else 0)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the CPU baseline")
     ap.add_argument("--aux", default=None, choices=sorted(AUX),
                     help="time ONE of the bandwidth-bound / auxiliary kernels and print its record (the command profiled under ncu)")

@@ -216,7 +216,7 @@ class ShardedGemm:
     """
 
     def __init__(self, M, N, K, dtype, group=None, owner=0, panels="ramp", gather=None, device=None, gemm_fn=None,
-                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push", owner_blocks_less=0, forward_d=True):
+                 reserve_sms=None, bcast=None, overlap=None, tile=0, scatter="push", owner_blocks_less=None, forward_d=True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -234,6 +234,10 @@ class ShardedGemm:
         # until the GEMM ends and the pipeline becomes broadcast-bound.
         self._reserve_arg = reserve_sms
         self.gather = gather or ("peer" if self.on_gpu and self.world > 1 else "collective")
+        if owner_blocks_less is None:
+            # the owner of B also sends B and receives everybody's D: at 8 GPUs it finishes with the others when it
+            # has two 256-row blocks fewer (4.04 vs 4.10, 4.07 vs 4.15, 3.98 vs 4.02 ms per step in three runs)
+            owner_blocks_less = 2 if (self.world >= 8 and overlap in (None, "fused")) else 0
         self.rows = row_ranges(M, self.world, lighter=(owner, owner_blocks_less) if owner_blocks_less else None)
         self.row0, self.nrows = self.rows[self.rank]
         self.panels = panel_plan(N, panels if self.world > 1 else 1)
