@@ -685,11 +685,15 @@ int dxb_host::conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsig
     p.conv_tiles_x = tiles_x;
     p.conv_kbi = kbi;
     p.b_chunked_map = 1;
-    // accumulator width: the narrowest of 64 / 128 / 256 columns that takes all kernels in one tile column (a wider
-    // tile re-reads the source tile less often, an over-wide one multiplies zeros)
+    // Tile: up to 64 kernels a single CTA with 64-column accumulators; beyond that CTA pairs (each CTA fetches its own
+    // 128 output positions and HALF of the kernel columns -- with hi and lo planes a single CTA could not pull a
+    // 128 x 128 tile's operands through its L2 port as fast as it multiplies them) with 128- or 256-column accumulators.
     const int bn = c.n <= 64 ? 64 : (c.n <= 128 ? 128 : 256);
+    static const int pair_env = [] { const char* e = getenv("DECXB200_CONV_PAIR"); return e ? atoi(e) : 1; }();
+    const bool pair = bn > 64 && pair_env != 0;
     const uint32_t chunks = bn == 64 ? GemmCfg<1, 1, 1, 0, 64>::B_CHUNKS
-                                     : (bn == 128 ? GemmCfg<1, 1, 1, 0, 128>::B_CHUNKS : GemmCfg<1, 1>::B_CHUNKS);
+                            : pair  ? (bn == 128 ? GemmCfg<1, 2, 1, 0, 128>::B_CHUNKS : GemmCfg<1, 2>::B_CHUNKS)
+                                    : (bn == 128 ? GemmCfg<1, 1, 1, 0, 128>::B_CHUNKS : GemmCfg<1, 1>::B_CHUNKS);
     using C1 = GemmCfg<1, 1>;
     CUtensorMap b0, b1;
     int rc;
@@ -699,9 +703,11 @@ int dxb_host::conv_tf32_implicit(cudaStream_t stream, const ConvPlanes& c, unsig
     if ((rc = make_map_b_chunked(&b1, false, c.b_lo, p.K, c.n, c.ldbw, C1::CHUNK_N, C1::BK, chunks,
                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != 0)
         return rc;
-    rc = bn == 64    ? launch_gemm<1, 1, 1, 0, 64>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
-         : bn == 128 ? launch_gemm<1, 1, 1, 0, 128>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d)
-                     : launch_gemm<1, 1>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    if (bn == 64) rc = launch_gemm<1, 1, 1, 0, 64>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    else if (pair && bn == 128) rc = launch_gemm<1, 2, 1, 0, 128>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    else if (pair) rc = launch_gemm<1, 2>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    else if (bn == 128) rc = launch_gemm<1, 1, 1, 0, 128>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
+    else rc = launch_gemm<1, 1>(stream, dev, a[0], a[1], b0, b1, p, 0, nullptr, true, &d);
     if (rc == 0) t_variant += 20000;
     return rc;
 }

@@ -111,9 +111,9 @@ struct GemmParams {
     //   [20] sum over the MMA threads of the time spent waiting for operands (full barriers), [21] ... for a free
     //   accumulator, [22] ... of their whole tile loops, [23] number of MMA threads counted
     unsigned long long* stats;
-    // Implicit-GEMM convolution (3xTF32 single-CTA kernels only; conv_tw == 0: an ordinary GEMM).  The 128 rows of
+    // Implicit-GEMM convolution (3xTF32 kernels; conv_tw == 0: an ordinary GEMM).  The 128 rows of
     // an M tile are a conv_tw x (128 / conv_tw) rectangle of output positions, row r = (r / conv_tw, r % conv_tw);
-    // tile index tm = ty * conv_tiles_x + tx.  The A maps are 4-D views of the zero-bordered source planes,
+    // tile index (tm * CTAS + rank of the CTA in its pair) = ty * conv_tiles_x + tx.  The A maps are 4-D views of the zero-bordered source planes,
     // (k within a kernel row, x, kernel row i, y): k-block kb is kernel row kb / conv_kbi, floats
     // [32 * (kb % conv_kbi), +32) of its kw * C contiguous floats.  The D map is 3-D (kernel, x, y).
     uint32_t conv_tw, conv_tiles_x, conv_kbi;
@@ -186,8 +186,8 @@ __device__ unsigned g_wave_ticket;
 
 template <int KIND, int CTAS, int NACC = 1, int FETCH = 0, int BNV = 256>
 struct GemmCfg {
-    static_assert(BNV == 256 || ((BNV == 64 || BNV == 128) && KIND == 1 && CTAS == 1),
-                  "narrow accumulators: 3xTF32 single-CTA tiles only");
+    static_assert(BNV == 256 || (BNV == 64 && KIND == 1 && CTAS == 1) || (BNV == 128 && KIND == 1),
+                  "narrow accumulators: 3xTF32 only (64 columns: single-CTA tiles)");
     static_assert(NACC == 1 || (NACC == 2 && KIND == 0 && CTAS == 2), "two accumulators per tile: fp16 CTA pairs only");
     static_assert(FETCH == 0 || (KIND == 0 && CTAS == 2), "courier warps: fp16 CTA pairs only");
     static constexpr int ELEM = (KIND == 0) ? 2 : 4;
@@ -679,10 +679,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 const int32_t row0 = int32_t((tm * CTAS + cta_rank) * Cfg::BM);
                 const int32_t col0 = int32_t(tn * Cfg::BN_TILE + cta_rank * Cfg::BN_LOAD);
                 int32_t conv_x0 = 0, conv_y0 = 0;
-                if constexpr (KIND == 1 && CTAS == 1) {
-                    if (p.conv_tw != 0) {
-                        conv_x0 = int32_t((tm % p.conv_tiles_x) * p.conv_tw);
-                        conv_y0 = int32_t((tm / p.conv_tiles_x) * (uint32_t(Cfg::BM) / p.conv_tw));
+                if constexpr (KIND == 1) {
+                    if (p.conv_tw != 0) {            // every CTA of a pair has an M tile of its own
+                        const uint32_t tmi = tm * CTAS + cta_rank;
+                        conv_x0 = int32_t((tmi % p.conv_tiles_x) * p.conv_tw);
+                        conv_y0 = int32_t((tmi / p.conv_tiles_x) * (uint32_t(Cfg::BM) / p.conv_tw));
                     }
                 }
                 for (uint32_t kb = 0; kb < n_kb; ++kb) {
@@ -701,7 +702,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         const CUtensorMap* mb = (pl == 0) ? &tmB0 : &tmB1;
                         const uint32_t a_dst = stage + pl * Cfg::A_TILE;
                         const uint32_t b_dst = stage + Cfg::NPL * Cfg::A_TILE + pl * Cfg::B_TILE;
-                        if constexpr (CTAS == 2) {
+                        if constexpr (CTAS == 2 && KIND == 1) {
+                            if (p.conv_tw != 0)
+                                tma_load_4d_pair(a_dst, ma, fb, int32_t((kb % p.conv_kbi) * Cfg::BK), conv_x0,
+                                                 int32_t(kb / p.conv_kbi), conv_y0);
+                            else
+                                tma_load_2d_pair(a_dst, ma, fb, k0, row0);
+                        } else if constexpr (CTAS == 2) {
                             tma_load_2d_pair(a_dst, ma, fb, k0, row0);
                         } else if constexpr (KIND == 1) {
                             if (p.conv_tw != 0)
@@ -979,13 +986,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                                 fence_proxy_async_smem();
                                 __syncwarp();
                                 if (lane == 0 && warp_row0 < p.M) {
-                                    bool conv = false;
-                                    if constexpr (CTAS == 1) conv = p.conv_tw != 0;
-                                    if (conv) {      // this warp's 32 rows: 32 consecutive x of one output row
-                                        const uint32_t r0 = quarter * 32;
+                                    if (p.conv_tw != 0) {   // this warp's 32 rows: 32 consecutive x of one output row
+                                        const uint32_t r0 = quarter * 32, tmi = tm * CTAS + cta_rank;
                                         tma_store_3d(&tmD, stage_warp, int32_t(col0),
-                                                     int32_t((tm % p.conv_tiles_x) * p.conv_tw + r0 % p.conv_tw),
-                                                     int32_t((tm / p.conv_tiles_x) * (uint32_t(Cfg::BM) / p.conv_tw) + r0 / p.conv_tw));
+                                                     int32_t((tmi % p.conv_tiles_x) * p.conv_tw + r0 % p.conv_tw),
+                                                     int32_t((tmi / p.conv_tiles_x) * (uint32_t(Cfg::BM) / p.conv_tw) + r0 / p.conv_tw));
                                     } else {
                                         tma_store_2d(&tmD, stage_warp, int32_t(col0), int32_t(warp_row0));
                                     }
