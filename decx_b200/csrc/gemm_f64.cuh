@@ -16,7 +16,10 @@
 
 namespace dxb {
 
-constexpr int F64_BM = 128, F64_BN = 128, F64_BK = 16, F64_STAGES = 3, F64_THREADS = 256;
+#ifndef DXB_F64_BK
+#define DXB_F64_BK 16
+#endif
+constexpr int F64_BM = 128, F64_BN = 128, F64_BK = DXB_F64_BK, F64_STAGES = 3, F64_THREADS = 256;
 constexpr int F64_LDA_S = F64_BK + 4;       // 20 doubles per row of the A tile
 constexpr int F64_LDB_S = F64_BN + 4;       // 132 doubles per row of the B tile
 constexpr int F64_A_STAGE = F64_BM * F64_LDA_S;
@@ -92,11 +95,12 @@ __global__ void __launch_bounds__(F64_THREADS, 1) gemm_f64_kernel(const GemmF64P
     const uint32_t n_kt = (p.K + F64_BK - 1) / F64_BK;
     auto issue = [&](uint32_t kt, uint32_t stage) {
         const uint32_t k0 = kt * F64_BK;
-        // A tile: 128 rows x 8 pairs; B tile: 16 rows x 64 pairs; 1024 pairs each, 4 per thread
+        // A tile: 128 rows x BK/2 pairs; B tile: BK rows x 64 pairs; 64 * BK pairs each, BK/4 per thread
+        constexpr uint32_t APR = F64_BK / 2;                // pairs per row of the A tile
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < F64_BK / 4; ++i) {
             const uint32_t c = tid + i * F64_THREADS;
-            const uint32_t ar = c >> 3, ap = (c & 7) * 2;
+            const uint32_t ar = c / APR, ap = (c % APR) * 2;
             load_pair(as_u32 + (stage * F64_A_STAGE + ar * F64_LDA_S + ap) * 8, p.A, p.lda, m0 + ar, k0 + ap, p.M, p.K,
                       p.vec_a);
             const uint32_t br = c >> 6, bp = (c & 63) * 2;
