@@ -461,6 +461,8 @@ def main():
     ap.add_argument("--gather", default=None, choices=[None, "peer", "collective"])
     ap.add_argument("--scatter", default=DEFAULT_SCATTER, choices=["push", "pull", "multicast"],
                     help="how B leaves the owner in the fused multi-GPU kernel")
+    ap.add_argument("--forward-d", action="store_true",
+                    help="multi-GPU: D leaves through a local ring and the courier warps (default at 2 GPUs only)")
     ap.add_argument("--direct-d", action="store_true",
                     help="multi-GPU: epilogues store D straight into the owner's memory (no forwarding by the couriers)")
     ap.add_argument("--owner-less", type=int, default=None,
@@ -537,7 +539,7 @@ def main():
     panels = args.panels if args.panels == "ramp" else int(args.panels)
     sg = ShardedGemm(M, N, K, tdtype, owner=0, panels=panels, gather=args.gather, device=device, bcast=args.bcast,
                      overlap=args.overlap, scatter=args.scatter, owner_blocks_less=args.owner_less,
-                     forward_d=not args.direct_d)
+                     forward_d=False if args.direct_d else (True if args.forward_d else None))
     if sg.nrows:
         sg.A.copy_(gen(torch, (sg.nrows, K), dtype, dist_name, sigma, device, 4 + 1000 * rank))
     if sg.is_owner:
