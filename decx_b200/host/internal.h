@@ -321,4 +321,115 @@ public:
     virtual ~_GPU_Vector();
 };
 
+// ------------------------------------------------------------------------------------------------ tensors
+// (reference: decx::_Tensor srcs/common/Classes/Tensor.h:59-82 + srcs/modules/core/classes/Tensor.cxx,
+// decx::_TensorArray TensorArray.cxx, decx::_GPU_Tensor GPU_Tensor.cu:35-140, decx::_GPU_TensorArray
+// srcs/common/Classes/GPU_TensorArray.h:115-200).  Channels innermost; see include/DECX/classes/tensors.h.
+_DECX_API_ void tensor_layout(de::TensorLayout& l, de::_DATA_TYPES_FLAGS_ t, uint32_t width, uint32_t height,
+                              uint32_t depth, uint32_t width_align);
+
+class _DECX_API_ _Tensor : public de::Tensor {
+public:
+    de::TensorLayout _layout;
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    bool _init = false, _pinned = false, _view = false;    // _view: a slice of a tensor array
+    uint64_t total_bytes = 0;
+    void* data = nullptr;            // 64-byte aligned, zero-filled
+    void* base = nullptr;            // start of the allocation `data` lies in (differs for a slice)
+    int* _shared = nullptr;          // owners of the allocation: tensors, slices and the array itself
+
+    _Tensor();
+    _Tensor(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth);
+
+    virtual uint32_t Width() const;
+    virtual uint32_t Height() const;
+    virtual uint32_t Depth() const;
+    virtual de::Tensor& SoftCopy(de::Tensor& src);
+    virtual void release();
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual ~_Tensor();
+};
+
+class _DECX_API_ _TensorArray : public de::TensorArray {
+public:
+    de::TensorLayout _layout;
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    uint32_t tensor_num = 0;
+    bool _init = false;
+    uint64_t _gap = 0, total_bytes = 0;     // elements between two tensors; bytes of all of them
+    void* data = nullptr;
+    void** ptrs = nullptr;                  // base pointer of every tensor (what ptr<T>() indexes)
+    int* _shared = nullptr;
+
+    _TensorArray();
+    _TensorArray(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth, uint32_t tensor_num);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth, uint32_t tensor_num);
+
+    virtual uint32_t Width() const;
+    virtual uint32_t Height() const;
+    virtual uint32_t Depth() const;
+    virtual uint32_t TensorNum() const;
+    virtual de::TensorArray& SoftCopy(de::TensorArray& src);
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual de::DH Extract_SoftCopy(const uint32_t index, de::Tensor& dst) const;
+    virtual void release();
+    virtual ~_TensorArray();
+};
+
+class _DECX_API_ _GPU_Tensor : public de::GPU_Tensor {
+public:
+    de::TensorLayout _layout;
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    bool _init = false;
+    uint64_t total_bytes = 0;
+    int _device = -1;
+    decx::PtrInfo<void> Tens;        // a slice of a tensor array shares the array's block (reference count)
+
+    _GPU_Tensor();
+    _GPU_Tensor(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth);
+    // new shape; re-allocates only if more bytes are needed (reference: GPU_Tensor.cu re_construct)
+    void re_construct(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth,
+                      decx::cuda_stream* S = nullptr);
+
+    virtual uint32_t Width() const;
+    virtual uint32_t Height() const;
+    virtual uint32_t Depth() const;
+    virtual de::GPU_Tensor& SoftCopy(de::GPU_Tensor& src);
+    virtual void release();
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual de::DH Extract_SoftCopy(const uint32_t index, de::GPU_Tensor& dst) const;
+    virtual ~_GPU_Tensor();
+};
+
+class _DECX_API_ _GPU_TensorArray : public de::GPU_TensorArray {
+public:
+    de::TensorLayout _layout;
+    de::_DATA_TYPES_FLAGS_ type = de::_VOID_;
+    uint32_t tensor_num = 0;
+    bool _init = false;
+    uint64_t _gap = 0, total_bytes = 0;     // elements between two tensors; bytes of all of them
+    int _device = -1;
+    decx::PtrInfo<void> TensArr;
+
+    _GPU_TensorArray();
+    _GPU_TensorArray(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth, uint32_t tensor_num);
+    void construct(const de::_DATA_TYPES_FLAGS_ type, uint32_t width, uint32_t height, uint32_t depth, uint32_t tensor_num);
+
+    virtual uint32_t Width() const;
+    virtual uint32_t Height() const;
+    virtual uint32_t Depth() const;
+    virtual uint32_t TensorNum() const;
+    virtual de::_DATA_TYPES_FLAGS_ Type() const;
+    virtual void Reinterpret(const de::_DATA_TYPES_FLAGS_ _new_type);
+    virtual de::GPU_TensorArray& SoftCopy(const de::GPU_TensorArray& src);
+    virtual de::DH Extract_SoftCopy(const uint32_t index, de::GPU_Tensor& dst) const;
+    virtual void release();
+    virtual ~_GPU_TensorArray();
+};
+
 }  // namespace decx

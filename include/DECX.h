@@ -10,7 +10,13 @@
 #include "DECX/classes/GPU_Matrix.h"
 #include "DECX/classes/Vector.h"
 #include "DECX/classes/GPU_Vector.h"
+#include "DECX/classes/Tensor.h"
+#include "DECX/classes/TensorArray.h"
+#include "DECX/classes/GPU_Tensor.h"
+#include "DECX/classes/GPU_TensorArray.h"
 #include "DECX/classes/decx_memcpy.h"
 #include "DECX/BLAS/BLAS.h"
 #include "DECX/basic_proc/type_cast.h"
+#include "DECX/basic_proc/VectorProc.h"
+#include "DECX/nn/convolution.h"
 #endif

@@ -31,5 +31,13 @@ struct __align__(8) Point2D {
     Point2D() {}
 };
 
+// {x = depth (channel), y = column, z = row} wherever a Point3D addresses a tensor
+struct __align__(16) Point3D {
+    int32_t x, y, z;
+    Point3D(const int32_t _x, const int32_t _y, const int32_t _z) : x(_x), y(_y), z(_z) {}
+    Point3D(const uint32_t _x, const uint32_t _y, const uint32_t _z) : x(int32_t(_x)), y(int32_t(_y)), z(int32_t(_z)) {}
+    Point3D() {}
+};
+
 }  // namespace de
 #endif

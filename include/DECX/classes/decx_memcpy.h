@@ -6,6 +6,8 @@
 #include "GPU_Matrix.h"
 #include "Vector.h"
 #include "GPU_Vector.h"
+#include "Tensor.h"
+#include "GPU_Tensor.h"
 
 namespace de {
 enum DECX_Memcpy_Flags { DECX_MEMCPY_H2D = 0, DECX_MEMCPY_D2H = 1 };
@@ -17,5 +19,8 @@ _DECX_API_ de::DH Memcpy(de::Matrix& __host, de::GPU_Matrix& __device, const de:
 // Vectors: cpy_size elements from index start_src of the source to index start_dst of the destination.
 _DECX_API_ de::DH Memcpy(de::Vector& __host, de::GPU_Vector& __device, const uint64_t start_src, const uint64_t start_dst,
                          const uint64_t cpy_size, const int _memcpy_flag);
+// Tensors: points are {x = channel, y = column, z = row}; cpy_size = {D, W, H}.
+_DECX_API_ de::DH Memcpy(de::Tensor& __host, de::GPU_Tensor& __device, const de::Point3D start_src,
+                         const de::Point3D start_dst, const de::Point3D cpy_size, const int _memcpy_flag);
 }  // namespace de
 #endif

@@ -245,8 +245,8 @@ DECXB200_API int decxb200_cast2d(int kind, void* stream, uint32_t rows, uint32_t
  * zero-bordered source with 4-D TMA boxes (implicit GEMM; workspace = those planes + the packed kernels, about twice
  * the source); otherwise the tf32 planes of the im2col matrix are written to the workspace first.  The workspace
  * query takes the destination pitch for that reason; a misaligned dst with a multiple-of-4 pitch needs the size the
- * query returns for an odd pitch.  The tensor containers (de::GPU_Tensor, de::GPU_TensorArray) are not part of this library: this
- * entry point is what the reference's conv2D_im2col_fp32_caller would bind.
+ * query returns for an odd pitch.  de::nn::cuda::Conv2D of the C++ drop-in (include/DECX/nn/convolution.h) is built
+ * on this entry point; it is also what the reference's conv2D_im2col_fp32_caller would bind.
  */
 #define DECXB200_EXTEND_NONE 0
 #define DECXB200_EXTEND_CONSTANT 2

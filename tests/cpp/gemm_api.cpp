@@ -411,6 +411,92 @@ static void concurrent_calls() {
     for (int t = 0; t < 4; ++t) CHECK(worst[t] <= 1.0);
 }
 
+// de::nn::cuda::Conv2D, the way samples/Conv2D/Conv2D.cpp drives it: host tensor and tensor array filled through
+// ptr<T>(), uploaded with de::Memcpy (the kernels slice by slice through Extract_SoftCopy), result downloaded and
+// compared with the direct sum in double.
+static void conv_case(uint32_t W, uint32_t H, uint32_t C, uint32_t kw, uint32_t kh, uint32_t n, int sx, int sy,
+                      de::extend_label ext) {
+    de::ResetLastError();
+    de::Tensor& src = de::CreateTensorRef(de::_FP32_, W, H, C);
+    de::TensorArray& ker = de::CreateTensorArrayRef(de::_FP32_, kw, kh, C, n);
+    for (uint32_t i = 0; i < H; ++i)
+        for (uint32_t j = 0; j < W; ++j)
+            for (uint32_t c = 0; c < C; ++c) *src.ptr<float>(i, j, c) = rnd();
+    for (uint32_t t = 0; t < n; ++t)
+        for (uint32_t i = 0; i < kh; ++i)
+            for (uint32_t j = 0; j < kw; ++j)
+                for (uint32_t c = 0; c < C; ++c) *ker.ptr<float>(i, j, c, t) = rnd();
+    de::GPU_Tensor& dsrc = de::CreateGPUTensorRef(de::_FP32_, W, H, C);
+    de::GPU_TensorArray& dker = de::CreateGPUTensorArrayRef(de::_FP32_, kw, kh, C, n);
+    de::GPU_Tensor& ddst = de::CreateGPUTensorRef();
+    CHECK(de::Memcpy(src, dsrc, {0, 0, 0}, {0, 0, 0}, de::Point3D(C, W, H), de::DECX_MEMCPY_H2D).error_type == de::DECX_SUCCESS);
+    de::Tensor& slice = de::CreateTensorRef();
+    de::GPU_Tensor& dslice = de::CreateGPUTensorRef();
+    for (uint32_t t = 0; t < n; ++t) {
+        CHECK(ker.Extract_SoftCopy(t, slice).error_type == de::DECX_SUCCESS);
+        CHECK(dker.Extract_SoftCopy(t, dslice).error_type == de::DECX_SUCCESS);
+        CHECK(de::Memcpy(slice, dslice, {0, 0, 0}, {0, 0, 0}, de::Point3D(C, kw, kh), de::DECX_MEMCPY_H2D).error_type ==
+              de::DECX_SUCCESS);
+    }
+    const de::DH h = de::nn::cuda::Conv2D(dsrc, dker, ddst, de::Point2D(sx, sy), ext);
+    CHECK(h.error_type == de::DECX_SUCCESS);
+    const uint32_t py = ext == de::_EXTEND_CONSTANT_ ? kh / 2 : 0, px = ext == de::_EXTEND_CONSTANT_ ? kw / 2 : 0;
+    const uint32_t OH = ext == de::_EXTEND_CONSTANT_ ? H / sy : (H - kh + 1) / sy;
+    const uint32_t OW = ext == de::_EXTEND_CONSTANT_ ? W / sx : (W - kw + 1) / sx;
+    const uint32_t hlim = ext == de::_EXTEND_CONSTANT_ ? OH * sy : H;
+    CHECK(ddst.Width() == OW && ddst.Height() == OH && ddst.Depth() == n && ddst.Type() == de::_FP32_);
+    if (h.error_type == de::DECX_SUCCESS && ddst.Width() == OW && ddst.Height() == OH) {
+        de::Tensor& dst = de::CreateTensorRef(de::_FP32_, OW, OH, n);
+        CHECK(de::Memcpy(dst, ddst, {0, 0, 0}, {0, 0, 0}, de::Point3D(n, OW, OH), de::DECX_MEMCPY_D2H).error_type ==
+              de::DECX_SUCCESS);
+        double worst = 0.0;
+        for (uint32_t y = 0; y < OH; ++y)
+            for (uint32_t x = 0; x < OW; ++x)
+                for (uint32_t t = 0; t < n; ++t) {
+                    double sum = 0.0, mag = 0.0;
+                    for (uint32_t i = 0; i < kh; ++i) {
+                        const int64_t yy = int64_t(y) * sy + i - py;
+                        if (yy < 0 || yy >= int64_t(hlim)) continue;
+                        for (uint32_t j = 0; j < kw; ++j) {
+                            const int64_t xx = int64_t(x) * sx + j - px;
+                            if (xx < 0 || xx >= int64_t(W)) continue;
+                            for (uint32_t c = 0; c < C; ++c) {
+                                const double p = double(*src.ptr<float>(int(yy), int(xx), c)) * double(*ker.ptr<float>(i, j, c, t));
+                                sum += p;
+                                mag += std::fabs(p);
+                            }
+                        }
+                    }
+                    const double err = std::fabs(double(*dst.ptr<float>(y, x, t)) - sum) / (mag + 1e-30);
+                    if (err > worst) worst = err;
+                }
+        CHECK(worst <= 1e-5);
+        dst.release();
+    }
+    // a second call with the same objects re-uses dst; a smaller problem keeps its block
+    CHECK(de::nn::cuda::Conv2D(dsrc, dker, ddst, de::Point2D(sx, sy), ext).error_type == de::DECX_SUCCESS);
+    src.release(); ker.release(); slice.release(); dslice.release(); dsrc.release(); dker.release(); ddst.release();
+}
+
+static void conv_cases() {
+    conv_case(33, 20, 8, 3, 3, 12, 1, 1, de::_EXTEND_CONSTANT_);      // implicit form, 64-column accumulators
+    conv_case(40, 31, 16, 5, 5, 4, 1, 1, de::_EXTEND_CONSTANT_);      // the sample's shape class: 5 x 5, four kernels
+    conv_case(21, 17, 3, 3, 2, 5, 2, 1, de::_EXTEND_NONE_);           // odd kernel count: materialised form
+    conv_case(64, 48, 32, 3, 3, 96, 1, 1, de::_EXTEND_NONE_);         // CTA pairs, 128-column accumulators
+    conv_case(30, 30, 4, 7, 7, 132, 2, 2, de::_EXTEND_CONSTANT_);     // more than 128 kernels, stride 2
+    // errors: depth mismatch, unsupported border mode, uninitialised operands
+    de::GPU_Tensor& s = de::CreateGPUTensorRef(de::_FP32_, 8, 8, 4);
+    de::GPU_TensorArray& k = de::CreateGPUTensorArrayRef(de::_FP32_, 3, 3, 8, 2);
+    de::GPU_Tensor& d = de::CreateGPUTensorRef();
+    CHECK(de::nn::cuda::Conv2D(s, k, d).error_type == de::DECX_FAIL_DimsNotMatching);
+    de::GPU_TensorArray& k2 = de::CreateGPUTensorArrayRef(de::_FP32_, 3, 3, 4, 2);
+    CHECK(de::nn::cuda::Conv2D(s, k2, d, de::Point2D(1, 1), de::_EXTEND_REFLECT_).error_type == de::DECX_FAIL_ErrorFlag);
+    de::GPU_TensorArray& k3 = de::CreateGPUTensorArrayRef(de::_FP32_, 9, 9, 4, 2);
+    CHECK(de::nn::cuda::Conv2D(s, k3, d).error_type == de::DECX_FAIL_DimsNotMatching);      // kernel larger than the source
+    CHECK(de::nn::cuda::Conv2D(d, k2, s).error_type == de::DECX_FAIL_CLASS_NOT_INIT);
+    s.release(); k.release(); k2.release(); k3.release();
+}
+
 int main() {
     de::InitCPUInfo();
     de::InitCuda();
@@ -432,6 +518,7 @@ int main() {
     }
     gemv_cases();
     transpose_cast_cases();
+    conv_cases();
     multi_gpu_host_case();
     concurrent_calls();
     sample_known_answer();

@@ -335,6 +335,97 @@ static void test_vectors() {
     p->release();
 }
 
+static void test_tensors() {
+    // layouts: channels innermost, depth padded to 16 bytes, width to 4 (host) / 8 (device) columns
+    CHECK(sizeof(de::Point3D) == 16);
+    de::TensorLayout l;
+    decx::tensor_layout(l, de::_FP32_, 13, 7, 3, 4);
+    CHECK(l.dpitch == 4 && l.wpitch == 16 && l.dp_x_wp == 64 && l._single_element_size == 4);
+    CHECK(l.plane[0] == 91 && l.plane[1] == 39 && l.plane[2] == 21);
+    decx::tensor_layout(l, de::_FP32_, 13, 7, 3, 8);
+    CHECK(l.dpitch == 4 && l.wpitch == 16);
+    decx::tensor_layout(l, de::_FP32_, 17, 7, 9, 8);
+    CHECK(l.dpitch == 12 && l.wpitch == 24);
+    decx::tensor_layout(l, de::_FP16_, 5, 2, 9, 4);
+    CHECK(l.dpitch == 16 && l.wpitch == 8);
+
+    de::Tensor& t = de::CreateTensorRef(de::_FP32_, 13, 7, 3);        // (type, WIDTH, HEIGHT, DEPTH)
+    CHECK(t.Width() == 13 && t.Height() == 7 && t.Depth() == 3 && t.Type() == de::_FP32_);
+    CHECK(*t.ptr<float>(6, 12, 2) == 0.f);                             // zero-filled; ptr(row, column, channel)
+    CHECK(t.ptr<float>(0, 1, 0) - t.ptr<float>(0, 0, 0) == 4);         // dpitch
+    CHECK(t.ptr<float>(1, 0, 0) - t.ptr<float>(0, 0, 0) == 64);        // dp_x_wp
+    *t.ptr<float>(6, 12, 2) = 7.f;
+    de::Tensor& u = de::CreateTensorRef();
+    u.SoftCopy(t);
+    t.release();
+    CHECK(u.Width() == 13 && *u.ptr<float>(6, 12, 2) == 7.f);         // shared storage outlives the first holder
+    u.release();
+
+    // host tensor array: tensors back to back; a slice is a view that keeps the storage alive
+    de::TensorArray& a = de::CreateTensorArrayRef(de::_FP32_, 5, 3, 6, 4);
+    CHECK(a.Width() == 5 && a.Height() == 3 && a.Depth() == 6 && a.TensorNum() == 4);
+    CHECK(a.ptr<float>(0, 0, 0, 1) - a.ptr<float>(0, 0, 0, 0) == 3 * 8 * 8);     // gap = height * wpitch * dpitch
+    *a.ptr<float>(2, 4, 5, 3) = 9.f;
+    de::Tensor& sl = de::CreateTensorRef();
+    CHECK(a.Extract_SoftCopy(3, sl).error_type == de::DECX_SUCCESS);
+    CHECK(sl.Width() == 5 && sl.Depth() == 6 && sl.ptr<float>(0, 0, 0) == a.ptr<float>(0, 0, 0, 3));
+    CHECK(a.Extract_SoftCopy(4, sl).error_type == de::DECX_FAIL_INVALID_PARAM);
+    a.release();
+    CHECK(*sl.ptr<float>(2, 4, 5) == 9.f);                             // the view outlives the array
+    sl.release();
+
+    // virtual slot order of the public interfaces
+    de::TensorArray* pa = de::CreateTensorArrayPtr(de::_FP32_, 2, 2, 4, 3);
+    void** vt = *reinterpret_cast<void***>(pa);
+    typedef uint32_t (*u32_fn)(const void*);
+    CHECK(reinterpret_cast<u32_fn>(vt[0])(pa) == 2 && reinterpret_cast<u32_fn>(vt[2])(pa) == 4 &&
+          reinterpret_cast<u32_fn>(vt[3])(pa) == 3);                   // Width, Depth, TensorNum
+    pa->release();
+
+    // device tensor array on the fake allocator (no zero-fill, nothing dereferenced): slices share the block
+    decx::MemPool_D::set_raw_allocator(fake_alloc, fake_free);
+    decx::MemPool_D* pool = decx::MemPool_D::GetInstance(0);
+    {
+        decx::_GPU_TensorArray arr;
+        arr.type = de::_FP32_;
+        arr.tensor_num = 3;
+        decx::tensor_layout(arr._layout, de::_FP32_, 5, 5, 16, 8);
+        arr._gap = arr._layout.dp_x_wp * 5;
+        arr.total_bytes = arr._gap * 3 * 4;
+        arr._device = 0;
+        CHECK(decx::alloc::_device_malloc(&arr.TensArr, arr.total_bytes, false) == 0);
+        arr._init = true;
+        CHECK(arr._gap == 5 * 8 * 16 && arr.Width() == 5 && arr.TensorNum() == 3);
+        decx::_GPU_Tensor s1, s2;
+        CHECK(arr.Extract_SoftCopy(1, s1).error_type == de::DECX_SUCCESS);
+        CHECK(arr.Extract_SoftCopy(2, s2).error_type == de::DECX_SUCCESS);
+        CHECK(arr.Extract_SoftCopy(3, s2).error_type == de::DECX_FAIL_INVALID_PARAM);
+        CHECK(static_cast<uint8_t*>(s1.Tens.ptr) - static_cast<uint8_t*>(arr.TensArr.ptr) == int64_t(arr._gap * 4));
+        CHECK(s1.Tens.block == arr.TensArr.block && arr.TensArr.block->refcount == 3);
+        CHECK(s1.Width() == 5 && s1.Depth() == 16 && s1._layout.wpitch == 8);
+        const uint64_t used = pool->bytes_in_use();
+        arr.release();
+        CHECK(pool->bytes_in_use() == used);                           // the slices keep the block
+        // re_construct of a slice must not write into the array's block: it drops the share and would allocate
+        s1.release();
+        CHECK(pool->bytes_in_use() == used);
+        s2.release();
+        CHECK(pool->bytes_in_use() == 0);
+    }
+    pool->release();
+    decx::MemPool_D::set_raw_allocator(nullptr, nullptr);
+
+    // the API refuses to run before de::InitCuda
+    de::GPU_Tensor& gs = de::CreateGPUTensorRef();
+    de::GPU_TensorArray& gk = de::CreateGPUTensorArrayRef();
+    de::GPU_Tensor& gd = de::CreateGPUTensorRef();
+    CHECK(de::nn::cuda::Conv2D(gs, gk, gd, de::Point2D(1, 1), de::_EXTEND_CONSTANT_).error_type == de::DECX_FAIL_CUDA_not_init);
+    de::Tensor& ht = de::CreateTensorRef(de::_FP32_, 2, 2, 4);
+    CHECK(de::Memcpy(ht, gs, de::Point3D(0, 0, 0), de::Point3D(0, 0, 0), de::Point3D(4, 2, 2), de::DECX_MEMCPY_H2D).error_type ==
+          de::DECX_FAIL_CUDA_not_init);
+    ht.release();
+}
+
 int main() {
     test_abi();
     test_pitch_and_host_matrix();
@@ -347,6 +438,7 @@ int main() {
     test_block_level_allocator();
     test_vectors();
     test_resource_lifespans();
+    test_tensors();
     if (g_fail == 0) std::printf("host_units: all checks passed\n");
     return g_fail == 0 ? 0 : 1;
 }

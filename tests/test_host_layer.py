@@ -59,11 +59,13 @@ def test_host_units_under_sanitizers(tmp_path, san):
     the collector thread and its users."""
     host = os.path.join(ROOT, "decx_b200", "host")
     cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-    srcs = [os.path.join(host, f) for f in sorted(os.listdir(host)) if f.endswith(".cpp") and f not in ("gemm_api.cpp", "blas_aux.cpp", "multi_gpu.cpp")]
+    srcs = [os.path.join(host, f) for f in sorted(os.listdir(host)) if f.endswith(".cpp") and f not in ("gemm_api.cpp", "blas_aux.cpp", "multi_gpu.cpp", "conv_api.cpp")]
     stub = tmp_path / "abi_stub.cpp"       # the unit tests call the GEMM entry only to see its "not initialised" error
     stub.write_text('#include "DECX.h"\n#include "decx_b200/host/internal.h"\n'
                     'void de::blas::cuda::GEMM(de::Matrix&, de::Matrix&, de::Matrix&) {\n'
                     '    decx::err::set(de::GetLastError(), de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first"); }\n'
+                    'de::DH de::nn::cuda::Conv2D(de::GPU_Tensor&, de::GPU_TensorArray&, de::GPU_Tensor&, const de::Point2D, const de::extend_label) {\n'
+                    '    de::DH h; decx::err::set(&h, de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first"); return h; }\n'
                     'void de::blas::cuda::GEMM(de::Matrix&, de::Matrix&, de::Matrix&, de::Matrix&) {\n'
                     '    decx::err::set(de::GetLastError(), de::DECX_FAIL_CUDA_not_init, "error: CUDA should be initialized first"); }\n')
     exe = str(tmp_path / "host_units_san")
