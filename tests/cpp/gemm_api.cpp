@@ -478,6 +478,37 @@ static void conv_case(uint32_t W, uint32_t H, uint32_t C, uint32_t kw, uint32_t 
     src.release(); ker.release(); slice.release(); dslice.release(); dsrc.release(); dker.release(); ddst.release();
 }
 
+// tensor de::Memcpy with corners: a {D, W, H} = {3, 4, 3} block from (channel 1, column 2, row 1) of a host tensor to
+// (channel 0, column 1, row 2) of a device tensor; the rest of the device tensor stays zero
+static void tensor_memcpy_case() {
+    de::ResetLastError();
+    de::Tensor& a = de::CreateTensorRef(de::_FP32_, 10, 6, 5);
+    for (uint32_t i = 0; i < 6; ++i)
+        for (uint32_t j = 0; j < 10; ++j)
+            for (uint32_t c = 0; c < 5; ++c) *a.ptr<float>(i, j, c) = float(100 * i + 10 * j + c + 1);
+    de::GPU_Tensor& g = de::CreateGPUTensorRef(de::_FP32_, 9, 7, 6);
+    CHECK(de::Memcpy(a, g, de::Point3D(1, 2, 1), de::Point3D(0, 1, 2), de::Point3D(3, 4, 3), de::DECX_MEMCPY_H2D).error_type ==
+          de::DECX_SUCCESS);
+    de::Tensor& b = de::CreateTensorRef(de::_FP32_, 9, 7, 6);
+    CHECK(de::Memcpy(b, g, de::Point3D(0, 0, 0), de::Point3D(0, 0, 0), de::Point3D(6, 9, 7), de::DECX_MEMCPY_D2H).error_type ==
+          de::DECX_SUCCESS);
+    int bad = 0;
+    for (uint32_t i = 0; i < 7; ++i)
+        for (uint32_t j = 0; j < 9; ++j)
+            for (uint32_t c = 0; c < 6; ++c) {
+                const bool in = i >= 2 && i < 5 && j >= 1 && j < 5 && c < 3;
+                const float want = in ? float(100 * (i - 2 + 1) + 10 * (j - 1 + 2) + (c + 1) + 1) : 0.f;
+                if (*b.ptr<float>(i, j, c) != want) ++bad;
+            }
+    CHECK(bad == 0);
+    CHECK(de::Memcpy(a, g, de::Point3D(3, 0, 0), de::Point3D(0, 0, 0), de::Point3D(3, 4, 3), de::DECX_MEMCPY_H2D).error_type ==
+          de::DECX_FAIL_MEMCPY_OVERRANGED);                       // channels 3..5 of a 5-channel source
+    de::GPU_Tensor& gh = de::CreateGPUTensorRef(de::_FP16_, 9, 7, 6);
+    CHECK(de::Memcpy(a, gh, de::Point3D(0, 0, 0), de::Point3D(0, 0, 0), de::Point3D(1, 1, 1), de::DECX_MEMCPY_H2D).error_type ==
+          de::MEMCPY_DIFFERENT_TYPES);
+    a.release(); b.release(); g.release(); gh.release();
+}
+
 static void conv_cases() {
     conv_case(33, 20, 8, 3, 3, 12, 1, 1, de::_EXTEND_CONSTANT_);      // implicit form, 64-column accumulators
     conv_case(40, 31, 16, 5, 5, 4, 1, 1, de::_EXTEND_CONSTANT_);      // the sample's shape class: 5 x 5, four kernels
@@ -518,6 +549,7 @@ int main() {
     }
     gemv_cases();
     transpose_cast_cases();
+    tensor_memcpy_case();
     conv_cases();
     multi_gpu_host_case();
     concurrent_calls();
