@@ -719,6 +719,7 @@ def main():
                 # single-call figure, host time included, stays beside it
                 ach = r.get("tflops_in_graph", r["tflops"])
                 r["roofline"] = {"bound": "tensor", "achieved": ach, "peak": wp, "unit": "TFLOP/s", "frac": ach / wp,
+                                 "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((w, 1)),
                                  "note": "whole call (pre-passes included) / measured bf16 burst"
                                  + ("" if WORKLOADS[w][0] == "float16" else " / 6")
                                  + ("; device time per call inside a replayed CUDA graph" if "tflops_in_graph" in r else "")}
@@ -740,7 +741,9 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from one ncu capture per kernel
 # (None = not captured for that configuration).  fp16 16384^3: 6.71 GB read + 0.53 GB written; config 5 has four
 # times the row slabs at the same N and K, so four times the traffic per launch; fp32 8192^3 from its own capture.
-TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 7.24e9, ("cfg5", 1): 29.0e9, ("cfg2", 1): 4.83e9}
+# fp32 fused 4099 x 3001 x 2053: 268.7 MB read + 48.2 MB written; fp32 1024^3: 16.8 MB read, D still in L2.
+TRAFFIC_BYTES_PER_LAUNCH = {("fp16_16384", 1): 7.24e9, ("cfg5", 1): 29.0e9, ("cfg2", 1): 4.83e9, ("cfg3", 1): 316.9e6,
+                            ("cfg1", 1): 16.8e6}
 
 if __name__ == "__main__":
     main()
